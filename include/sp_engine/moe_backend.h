@@ -1,0 +1,138 @@
+/* moe_backend.h — C ABI of libsp_moe_b200: the Gemma-4-26B-A4B mixture-of-experts feed-forward
+ * layer (router softmax top-NU over NE experts, Q4B expert gate|up GeGLU + down, the always-on
+ * shared expert, ordered weighted combine, sandwich norms) as hand-written sm_100a kernels with
+ * every expert resident in device memory.
+ *
+ * It replaces, behind the same conventions, what the kairos-engine CUDA backend does inside
+ * src/backends/cuda/cuda_forward.cu (cited below as CF):
+ *   g4_ffn_block -> g4_ffn_apply(moe_on=1)           CF:9101-9114, 8314-9050   -> sp_moe_forward*
+ *   build_weights (MoE part), moe_cache_init,
+ *   moe_resident, moe_expert_view                     CF:2222-2372, 6773-6951, 6184-6193 -> sp_moe_open / sp_moe_upload_layer*
+ *   gemma4_moe_ffn_q4b_cuda (standalone operator)     CF:13821-13977           -> same symbol, same signature
+ *   sp_cuda_model_release                             CF:16103-16107           -> sp_moe_close
+ *
+ * Conventions (include/sp_engine/sp_status.h:18-59, CF:187-202): every entry returns int,
+ * 0 = success, negative sp_status value on error, with the detail in the thread-local
+ * sp_last_error(). Callers own every host buffer they pass; the handle owns all device memory.
+ * A handle is not thread-safe (the reference's callers hold a per-session mutex,
+ * tools/sp_daemon/src/cuda_kvdecode_dispatch.rs:400-401); different handles may be used
+ * concurrently. There is no CPU fallback: without a CUDA device every call fails.
+ */
+#ifndef SP_ENGINE_MOE_BACKEND_H
+#define SP_ENGINE_MOE_BACKEND_H
+#include <stdint.h>
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status values used here; numerically those of include/sp_engine/sp_status.h */
+#define SP_MOE_OK            0
+#define SP_MOE_ENOMEM      (-1)
+#define SP_MOE_EBADARG     (-3)
+#define SP_MOE_EBADSTATE   (-4)
+#define SP_MOE_EUNSUPPORTED (-5)
+#define SP_MOE_ECUDA      (-40)
+#define SP_MOE_EBACKEND_OOM (-43)
+
+/* Thread-local error text of the last failing call on this thread (sp_status.h:57-59).
+ * Exported WEAK so that, when linked into the daemon, the math core's definitions win. */
+const char *sp_last_error(void);
+void        sp_set_error(const char *msg);
+
+typedef struct sp_moe sp_moe;          /* opaque; replaces the engine-owned g_w MoE fields, CF:1856-1903 */
+
+/* Arithmetic the forward runs in (the AMMD switch, CF:8322-8324). */
+#define SP_MOE_FLAVOUR_DECODE  0   /* int8 per-16 activation quant + exact integer dots (decode, M small) */
+#define SP_MOE_FLAVOUR_PREFILL 1   /* exact Q4B dequant, floating-point GEMM (prefill, M large) */
+
+typedef struct {
+    int32_t E;           /* hidden size; multiple of 32, <= 8192 */
+    int32_t NE;          /* routed experts per layer, <= 1024 */
+    int32_t NU;          /* experts used per token, <= 8 (G4G_MAX, CF:5989) */
+    int32_t FFE;         /* routed expert FFN width; multiple of 32 */
+    int32_t FFS;         /* shared expert FFN width; multiple of 32 */
+    int32_t n_layers;
+    int32_t max_tokens;  /* largest M a forward call may pass */
+    int32_t device;      /* CUDA device ordinal */
+    float   eps;
+    int32_t reserved[7]; /* zero */
+} sp_moe_config;
+
+/* One layer's weights in the reference's layouts (sp_model.h:50-53, CF:1448-1464, 6179-6193):
+ * Q4B codes are row-major, in/2 bytes per row, byte k = weight 2k (low nibble) | weight 2k+1
+ * (high nibble), 4-bit two's complement; block scales are f16 bit patterns [rows][in/32].
+ * gate|up is ONE fused tensor of NE*2*FFE rows (expert e owns rows [e*2*FFE, (e+1)*2*FFE),
+ * gate first, then up); down is NE*E rows of FFE columns. */
+typedef struct {
+    const float    *router_w;      /* [NE][E] f32, CF:2258-2268 */
+    const float    *router_scale;  /* [E]   ffn_gate_inp.scale */
+    const float    *router_bias;   /* [NE]  optional, may be NULL (added to the logits) */
+    const float    *ffn_norm, *post_ffw1, *pre_ffw2, *post_ffw2, *post_ffw;   /* [E] */
+    const float    *dexps_scale;   /* [NE]  ffn_down_exps.scale, CF:1873-1878 */
+    const uint8_t  *gu_codes;  const uint16_t *gu_bs;
+    const uint8_t  *dn_codes;  const uint16_t *dn_bs;
+    const uint8_t  *sg_codes;  const uint16_t *sg_bs;   /* shared gate [FFS][E] */
+    const uint8_t  *su_codes;  const uint16_t *su_bs;   /* shared up   [FFS][E] */
+    const uint8_t  *sd_codes;  const uint16_t *sd_bs;   /* shared down [E][FFS] */
+} sp_moe_layer_weights;
+
+/* gemma4_kv_open's MoE share (CF:9807 -> build_weights CF:2222-2372 -> moe_cache_init
+ * CF:6773-6879): allocates one resident arena for all n_layers * NE experts plus scratch. */
+int  sp_moe_open(const sp_moe_config *cfg, sp_moe **out);
+/* sp_cuda_model_release, CF:16103-16107. NULL-safe. */
+int  sp_moe_close(sp_moe *h);
+/* Copies one layer into the arena (moe_stage without the cache, CF:9065-9099). The pointers
+ * are HOST memory in sp_moe_upload_layer and DEVICE memory in sp_moe_upload_layer_dev. */
+int  sp_moe_upload_layer(sp_moe *h, int layer, const sp_moe_layer_weights *w);
+int  sp_moe_upload_layer_dev(sp_moe *h, int layer, const sp_moe_layer_weights *w);
+/* Bytes of device memory the handle holds (arena + scratch). */
+size_t sp_moe_device_bytes(const sp_moe *h);
+
+/* g4_ffn_apply (CF:8314-9050) over layers [layer_first, layer_first + n_layers): each layer's
+ * output residual feeds the next. x, y: [M][E] f32; sel: [n_layers][M][NU] expert ids in
+ * descending probability (moe_topk_host order, CF:6220-6240); wts: the matching renormalised
+ * probabilities. sel / wts may be NULL. HOST pointers; copies in, runs, copies out, synchronises. */
+int  sp_moe_forward(sp_moe *h, int layer_first, int n_layers, int flavour, int M,
+                    const float *x, float *y, int32_t *sel, float *wts);
+/* Same with DEVICE pointers on a caller stream (a cudaStream_t passed as void*); enqueues only.
+ * A router row with a NaN (the reference's hard error, CF:8596-8620) is reported by the next
+ * sp_moe_status call. */
+int  sp_moe_forward_dev(sp_moe *h, int layer_first, int n_layers, int flavour, int M,
+                        const float *x_dev, float *y_dev, int32_t *sel_dev, float *wts_dev,
+                        void *stream);
+/* Synchronises the handle's last stream and returns 0 or the error a kernel recorded. */
+int  sp_moe_status(sp_moe *h);
+
+/* The reference's standalone single-token operator, verbatim signature (CF:13821-13825).
+ * All pointers are HOST memory; allocates, uploads the whole expert set, runs, frees.
+ * Its semantics differ from the layer above (one weightless norm, no shared expert, no
+ * clamp, descending-probability accumulation; CF:13821-13977). Returns 0, or 1 on error. */
+int gemma4_moe_ffn_q4b_cuda(int E, int NE, int NU, int FF, float eps,
+                            const float *gate_inp, const float *gate_inp_scale,
+                            const unsigned char *gu_codes, const unsigned short *gu_bscale,
+                            const unsigned char *dn_codes, const unsigned short *dn_bscale,
+                            const float *hidden, float *out, int *sel_out);
+
+/* Q4B block quantiser on DEVICE memory: the recipe of sp_model.h:50-53 / CF:1680-1687 (per-32
+ * block, f16 scale stored first, codes derived against the stored scale, codes in [-7,7]).
+ * The reference's own quantiser is in a submodule that is not part of its tree; this follows
+ * the documented recipe only. w: [rows][cols] f32; codes: [rows][cols/2]; bs: [rows][cols/32]. */
+int sp_moe_q4b_quantize_dev(const float *w_dev, int64_t rows, int cols,
+                            uint8_t *codes_dev, uint16_t *bs_dev, void *stream);
+/* k_dequant_arena_q4b, CF:1452-1464. */
+int sp_moe_q4b_dequantize_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int64_t rows, int cols,
+                              float *w_dev, void *stream);
+
+/* k_gelu_mul (CF:1364-1373): out[i] = gelu_tanh(g[i]) * up[i] on DEVICE memory, in the library's
+ * bit-reproducible arithmetic (the tanh is a fixed sequence of correctly-rounded operations). */
+int sp_moe_gelu_mul_dev(const float *g_dev, const float *up_dev, int64_t n, float *out_dev, void *stream);
+
+/* Counters for callers that report them (the reference prints similar lines under SP_MOE_TIMING,
+ * CF:9020-9044): kernels launched by this handle since open. */
+uint64_t sp_moe_kernel_launches(const sp_moe *h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SP_ENGINE_MOE_BACKEND_H */

@@ -1,0 +1,276 @@
+/* api.cu — the extern "C" surface of libsp_moe_b200 (include/sp_engine/moe_backend.h).
+ *
+ * Holds what the reference keeps in process globals (g_w MoE fields CF:1856-1903, the expert
+ * cache CF:6773-6951, g4_moe_scratch CF:5547) inside one handle: a single resident arena with
+ * every layer's router, norm vectors, shared expert and all NE routed experts, plus scratch.
+ * With all experts resident, moe_resident's hit branch (pointer arithmetic, CF:6923-6942) is
+ * the only branch left. CF = src/backends/cuda/cuda_forward.cu of nihilistau/kairos-engine.
+ */
+#include "common.cuh"
+#include "decode.cuh"
+#include "batched.cuh"
+#include "../../include/sp_engine/moe_backend.h"
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+/* ---------------------------------------------------------------- error text (sp_status.h:57-59) */
+static thread_local char g_err[768];
+extern "C" __attribute__((weak)) void sp_set_error(const char *msg) {
+    std::snprintf(g_err, sizeof g_err, "%s", msg ? msg : "");
+}
+extern "C" __attribute__((weak)) const char *sp_last_error(void) { return g_err; }
+
+static int fail(int code, const char *fmt, ...) {
+    char b[640];
+    va_list ap; va_start(ap, fmt); std::vsnprintf(b, sizeof b, fmt, ap); va_end(ap);
+    sp_set_error(b);
+    return code;
+}
+static int fail_cuda(cudaError_t e, const char *where) {       /* CF:189-195 */
+    const int code = (e == cudaErrorMemoryAllocation) ? SP_MOE_EBACKEND_OOM : SP_MOE_ECUDA;
+    return fail(code, "CUDA: %s: %s (%d)", where, cudaGetErrorString(e), (int)e);
+}
+#define CK(call, where) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail_cuda(e_, where); } while (0)
+
+/* ---------------------------------------------------------------- handle */
+struct LayerOffsets {           /* byte offsets into the arena */
+    size_t router_w, router_scale, router_bias, ffn_norm, post_ffw1, pre_ffw2, post_ffw2, post_ffw, dexps_scale;
+    size_t gu_codes, gu_bs, dn_codes, dn_bs, sg_codes, sg_bs, su_codes, su_bs, sd_codes, sd_bs;
+    size_t end;
+};
+
+struct sp_moe {
+    sp_moe_config cfg;
+    SpDims d;
+    int device;
+    unsigned char *arena;       /* all layers, contiguous */
+    size_t arena_bytes, layer_bytes;
+    LayerOffsets off;           /* offsets inside one layer's slab */
+    SpLayerDev *layers_dev;     /* device array [n_layers] */
+    std::vector<SpLayerDev> layers_host;
+    std::vector<unsigned char> has_bias, uploaded;
+    /* decode scratch */
+    float *logits, *hd, *dn, *hbuf, *acc;
+    unsigned *bar; int *status;
+    unsigned bar_epoch;
+    int dec_grid; size_t dec_smem;
+    /* host-pointer entry staging */
+    float *x_dev, *y_dev; int32_t *sel_dev; float *wts_dev;
+    SpBatchedScratch bs;
+    cudaStream_t stream;        /* stream of the host-pointer entry */
+    cudaStream_t last_stream;
+    size_t scratch_bytes;
+    uint64_t launches;
+};
+
+static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static void layout(const sp_moe_config &c, LayerOffsets &o) {
+    size_t p = 0;
+    auto take = [&](size_t bytes) { size_t at = p; p = up256(p + bytes); return at; };
+    const size_t E = c.E, NE = c.NE, FFE = c.FFE, FFS = c.FFS;
+    o.router_w = take(4 * NE * E); o.router_scale = take(4 * E); o.router_bias = take(4 * NE);
+    o.ffn_norm = take(4 * E); o.post_ffw1 = take(4 * E); o.pre_ffw2 = take(4 * E);
+    o.post_ffw2 = take(4 * E); o.post_ffw = take(4 * E); o.dexps_scale = take(4 * NE);
+    o.sg_codes = take(FFS * E / 2); o.sg_bs = take(2 * FFS * (E / 32));
+    o.su_codes = take(FFS * E / 2); o.su_bs = take(2 * FFS * (E / 32));
+    o.sd_codes = take(E * FFS / 2); o.sd_bs = take(2 * E * (FFS / 32));
+    o.gu_codes = take(NE * 2 * FFE * E / 2); o.gu_bs = take(2 * NE * 2 * FFE * (E / 32));
+    o.dn_codes = take(NE * E * FFE / 2); o.dn_bs = take(2 * NE * E * (FFE / 32));
+    o.end = p;
+}
+
+static SpLayerDev layer_view(const sp_moe *h, int L, bool bias) {
+    unsigned char *b = h->arena + (size_t)L * h->layer_bytes;
+    const LayerOffsets &o = h->off;
+    SpLayerDev v;
+    v.router_w = (const float *)(b + o.router_w); v.router_scale = (const float *)(b + o.router_scale);
+    v.router_bias = bias ? (const float *)(b + o.router_bias) : nullptr;
+    v.ffn_norm = (const float *)(b + o.ffn_norm); v.post_ffw1 = (const float *)(b + o.post_ffw1);
+    v.pre_ffw2 = (const float *)(b + o.pre_ffw2); v.post_ffw2 = (const float *)(b + o.post_ffw2);
+    v.post_ffw = (const float *)(b + o.post_ffw); v.dexps_scale = (const float *)(b + o.dexps_scale);
+    v.gu_codes = b + o.gu_codes; v.gu_bs = (const uint16_t *)(b + o.gu_bs);
+    v.dn_codes = b + o.dn_codes; v.dn_bs = (const uint16_t *)(b + o.dn_bs);
+    v.sg_codes = b + o.sg_codes; v.sg_bs = (const uint16_t *)(b + o.sg_bs);
+    v.su_codes = b + o.su_codes; v.su_bs = (const uint16_t *)(b + o.su_bs);
+    v.sd_codes = b + o.sd_codes; v.sd_bs = (const uint16_t *)(b + o.sd_bs);
+    return v;
+}
+
+extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
+    if (!cfg || !out) return fail(SP_MOE_EBADARG, "sp_moe_open: NULL argument");
+    *out = nullptr;
+    const sp_moe_config &c = *cfg;
+    if (c.E <= 0 || (c.E & 31) || c.E > 4096 || c.FFE <= 0 || (c.FFE & 31) || c.FFE > 4096 ||
+        c.FFS <= 0 || (c.FFS & 31) || c.FFS > 4096)                                  /* CF:13828; moe_cpu_expert.c:243 */
+        return fail(SP_MOE_EBADARG, "sp_moe_open: E, FFE, FFS must be multiples of 32 in (0, 4096] (got %d, %d, %d)", c.E, c.FFE, c.FFS);
+    if (c.NE <= 0 || c.NE > 1024 || c.NU <= 0 || c.NU > SP_MAX_NU || c.NU > c.NE)
+        return fail(SP_MOE_EBADARG, "sp_moe_open: need 0 < NU <= min(NE, %d), NE <= 1024 (got NE=%d NU=%d)", SP_MAX_NU, c.NE, c.NU);
+    if (c.n_layers <= 0 || c.max_tokens <= 0) return fail(SP_MOE_EBADARG, "sp_moe_open: n_layers and max_tokens must be positive");
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) { cudaGetLastError(); return fail(SP_MOE_ECUDA, "sp_moe_open: no CUDA device (%s); this library has no CPU path", cudaGetErrorString(e)); }
+    if (c.device < 0 || c.device >= ndev) return fail(SP_MOE_EBADARG, "sp_moe_open: device %d out of range (%d present)", c.device, ndev);
+    CK(cudaSetDevice(c.device), "cudaSetDevice");
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, c.device), "cudaGetDeviceProperties");
+    if (prop.major != 10) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: built for sm_100a only; device is sm_%d%d", prop.major, prop.minor);
+
+    sp_moe *h = new (std::nothrow) sp_moe();
+    if (!h) return fail(SP_MOE_ENOMEM, "sp_moe_open: host OOM");
+    h->cfg = c; h->device = c.device;
+    h->d.E = c.E; h->d.NE = c.NE; h->d.NU = c.NU; h->d.FFE = c.FFE; h->d.FFS = c.FFS; h->d.eps = c.eps;
+    h->d.inv_sqrt_e = 1.0f / sqrtf((float)c.E);
+    layout(c, h->off);
+    h->layer_bytes = h->off.end;
+    h->arena_bytes = h->layer_bytes * (size_t)c.n_layers;
+    h->layers_host.resize(c.n_layers); h->has_bias.assign(c.n_layers, 0); h->uploaded.assign(c.n_layers, 0);
+#define OPEN_CK(call, where) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { int rc_ = fail_cuda(e_, where); sp_moe_close(h); return rc_; } } while (0)
+    OPEN_CK(cudaMalloc(&h->arena, h->arena_bytes), "arena cudaMalloc");
+    OPEN_CK(cudaMalloc(&h->layers_dev, sizeof(SpLayerDev) * c.n_layers), "layer table cudaMalloc");
+    for (int L = 0; L < c.n_layers; L++) h->layers_host[L] = layer_view(h, L, false);
+    OPEN_CK(cudaMemcpy(h->layers_dev, h->layers_host.data(), sizeof(SpLayerDev) * c.n_layers, cudaMemcpyHostToDevice), "layer table H2D");
+    size_t sb = 0;
+    auto dalloc = [&](void **p, size_t bytes) { sb += up256(bytes); return cudaMalloc(p, bytes); };
+    OPEN_CK(dalloc((void **)&h->logits, 4 * (size_t)c.NE), "scratch"); OPEN_CK(dalloc((void **)&h->hd, 4 * (size_t)c.FFS), "scratch");
+    OPEN_CK(dalloc((void **)&h->dn, 4 * (size_t)c.E), "scratch"); OPEN_CK(dalloc((void **)&h->hbuf, 4 * (size_t)c.NU * c.FFE), "scratch");
+    OPEN_CK(dalloc((void **)&h->acc, 4 * (size_t)c.E), "scratch");
+    OPEN_CK(dalloc((void **)&h->bar, 256), "scratch"); OPEN_CK(dalloc((void **)&h->status, 256), "scratch");
+    OPEN_CK(cudaMemset(h->bar, 0, 256), "memset"); OPEN_CK(cudaMemset(h->status, 0, 256), "memset");
+    const size_t mt = (size_t)c.max_tokens;
+    OPEN_CK(dalloc((void **)&h->x_dev, 4 * mt * c.E), "staging"); OPEN_CK(dalloc((void **)&h->y_dev, 4 * mt * c.E), "staging");
+    OPEN_CK(dalloc((void **)&h->sel_dev, 4 * mt * c.NU * c.n_layers), "staging"); OPEN_CK(dalloc((void **)&h->wts_dev, 4 * mt * c.NU * c.n_layers), "staging");
+    { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
+    OPEN_CK(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking), "cudaStreamCreate");
+    h->last_stream = h->stream;
+    h->scratch_bytes = sb;
+    /* persistent decode kernel: one CTA per SM, co-resident */
+    {
+        int sms = 0; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
+        h->dec_smem = sp_decode_smem_bytes(h->d, sms);
+        int grid = 0;
+        OPEN_CK(sp_decode_prepare(h->dec_smem, &grid), "decode kernel attributes");
+        if (grid <= 0) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM (%zu B shared memory)", h->dec_smem); }
+        h->dec_grid = grid;
+    }
+#undef OPEN_CK
+    *out = h;
+    return SP_MOE_OK;
+}
+
+extern "C" int sp_moe_close(sp_moe *h) {
+    if (!h) return SP_MOE_OK;
+    cudaSetDevice(h->device);
+    if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
+    sp_batched_free(&h->bs);
+    void *ps[] = {h->arena, h->layers_dev, h->logits, h->hd, h->dn, h->hbuf, h->acc, h->bar, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
+    for (void *p : ps) if (p) cudaFree(p);
+    cudaGetLastError();
+    delete h;
+    return SP_MOE_OK;
+}
+
+extern "C" size_t sp_moe_device_bytes(const sp_moe *h) { return h ? h->arena_bytes + h->scratch_bytes : 0; }
+extern "C" uint64_t sp_moe_kernel_launches(const sp_moe *h) { return h ? h->launches : 0; }
+
+static int upload(sp_moe *h, int L, const sp_moe_layer_weights *w, cudaMemcpyKind kind, const char *who) {
+    if (!h || !w) return fail(SP_MOE_EBADARG, "%s: NULL argument", who);
+    if (L < 0 || L >= h->cfg.n_layers) return fail(SP_MOE_EBADARG, "%s: layer %d out of range [0, %d)", who, L, h->cfg.n_layers);
+    const void *req[] = {w->router_w, w->router_scale, w->ffn_norm, w->post_ffw1, w->pre_ffw2, w->post_ffw2, w->post_ffw, w->dexps_scale,
+                         w->gu_codes, w->gu_bs, w->dn_codes, w->dn_bs, w->sg_codes, w->sg_bs, w->su_codes, w->su_bs, w->sd_codes, w->sd_bs};
+    for (const void *p : req) if (!p) return fail(SP_MOE_EBADARG, "%s: a MoE weight/norm/scale pointer is NULL at L=%d", who, L);   /* CF:8386-8393 */
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    unsigned char *b = h->arena + (size_t)L * h->layer_bytes;
+    const LayerOffsets &o = h->off;
+    const size_t E = h->cfg.E, NE = h->cfg.NE, FFE = h->cfg.FFE, FFS = h->cfg.FFS;
+#define UP(off, src, bytes) CK(cudaMemcpy(b + (off), (src), (bytes), kind), who)
+    UP(o.router_w, w->router_w, 4 * NE * E); UP(o.router_scale, w->router_scale, 4 * E);
+    if (w->router_bias) UP(o.router_bias, w->router_bias, 4 * NE);
+    UP(o.ffn_norm, w->ffn_norm, 4 * E); UP(o.post_ffw1, w->post_ffw1, 4 * E); UP(o.pre_ffw2, w->pre_ffw2, 4 * E);
+    UP(o.post_ffw2, w->post_ffw2, 4 * E); UP(o.post_ffw, w->post_ffw, 4 * E); UP(o.dexps_scale, w->dexps_scale, 4 * NE);
+    UP(o.sg_codes, w->sg_codes, FFS * E / 2); UP(o.sg_bs, w->sg_bs, 2 * FFS * (E / 32));
+    UP(o.su_codes, w->su_codes, FFS * E / 2); UP(o.su_bs, w->su_bs, 2 * FFS * (E / 32));
+    UP(o.sd_codes, w->sd_codes, E * FFS / 2); UP(o.sd_bs, w->sd_bs, 2 * E * (FFS / 32));
+    UP(o.gu_codes, w->gu_codes, NE * 2 * FFE * E / 2); UP(o.gu_bs, w->gu_bs, 2 * NE * 2 * FFE * (E / 32));
+    UP(o.dn_codes, w->dn_codes, NE * E * FFE / 2); UP(o.dn_bs, w->dn_bs, 2 * NE * E * (FFE / 32));
+#undef UP
+    h->has_bias[L] = w->router_bias != nullptr;
+    h->layers_host[L] = layer_view(h, L, h->has_bias[L]);
+    CK(cudaMemcpy(h->layers_dev + L, &h->layers_host[L], sizeof(SpLayerDev), cudaMemcpyHostToDevice), who);
+    h->uploaded[L] = 1;
+    return SP_MOE_OK;
+}
+extern "C" int sp_moe_upload_layer(sp_moe *h, int L, const sp_moe_layer_weights *w) { return upload(h, L, w, cudaMemcpyHostToDevice, "sp_moe_upload_layer"); }
+extern "C" int sp_moe_upload_layer_dev(sp_moe *h, int L, const sp_moe_layer_weights *w) { return upload(h, L, w, cudaMemcpyDeviceToDevice, "sp_moe_upload_layer_dev"); }
+
+/* ---------------------------------------------------------------- forward */
+static int check_forward(sp_moe *h, int lf, int nl, int flavour, int M, const void *x, const void *y, const char *who) {
+    if (!h || !x || !y) return fail(SP_MOE_EBADARG, "%s: NULL argument", who);
+    if (lf < 0 || nl <= 0 || lf + nl > h->cfg.n_layers) return fail(SP_MOE_EBADARG, "%s: layers [%d, %d) outside [0, %d)", who, lf, lf + nl, h->cfg.n_layers);
+    if (M <= 0 || M > h->cfg.max_tokens) return fail(SP_MOE_EBADARG, "%s: M=%d outside (0, max_tokens=%d]", who, M, h->cfg.max_tokens);
+    if (flavour != SP_MOE_FLAVOUR_DECODE && flavour != SP_MOE_FLAVOUR_PREFILL) return fail(SP_MOE_EBADARG, "%s: unknown flavour %d", who, flavour);
+    for (int L = lf; L < lf + nl; L++) if (!h->uploaded[L]) return fail(SP_MOE_EBADSTATE, "%s: layer %d has no weights uploaded", who, L);
+    return SP_MOE_OK;
+}
+
+extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
+                                  const float *x_dev, float *y_dev, int32_t *sel_dev, float *wts_dev, void *stream) {
+    int rc = check_forward(h, lf, nl, flavour, M, x_dev, y_dev, "sp_moe_forward_dev");
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream;
+    h->last_stream = st;
+    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
+        SpDecodeArgs a;
+        a.layers = h->layers_dev; a.layer_first = lf; a.n_layers = nl; a.d = h->d;
+        a.x_in = x_dev; a.y_out = y_dev; a.sel_out = sel_dev; a.wts_out = wts_dev;
+        a.logits = h->logits; a.hd = h->hd; a.dn = h->dn; a.h = h->hbuf; a.acc = h->acc;
+        a.bar = h->bar; a.status = h->status; a.bar_base = h->bar_epoch;
+        h->bar_epoch += (unsigned)(h->dec_grid * sp_decode_barriers_per_layer() * nl);
+        CK(sp_decode_launch(a, h->dec_grid, h->dec_smem, st), "decode kernel launch");
+        h->launches += 1;
+        return SP_MOE_OK;
+    }
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_forward(h->d, h->layers_dev, lf, nl, flavour, M, x_dev, y_dev, sel_dev, wts_dev, &h->bs, h->status, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    if (e != cudaSuccess) return fail_cuda(e, "batched forward launch");
+    return SP_MOE_OK;
+}
+
+extern "C" int sp_moe_status(sp_moe *h) {
+    if (!h) return fail(SP_MOE_EBADARG, "sp_moe_status: NULL handle");
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    CK(cudaStreamSynchronize(h->last_stream), "stream synchronize");
+    int st = 0;
+    CK(cudaMemcpy(&st, h->status, sizeof st, cudaMemcpyDeviceToHost), "status D2H");
+    if (st == SP_KERR_NONE) return SP_MOE_OK;
+    cudaMemset(h->status, 0, sizeof(int));
+    if (st == SP_KERR_BARRIER_TIMEOUT) {            /* counters are no longer consistent: start over */
+        cudaMemset(h->bar, 0, 256); h->bar_epoch = 0;
+        return fail(SP_MOE_ECUDA, "gemma4-MoE: a grid barrier wait ran out; the step's output is invalid");
+    }
+    if (st == SP_KERR_NAN_ROUTER)                     /* CF:8596-8620 */
+        return fail(SP_MOE_EBADSTATE, "gemma4-MoE: router produced no usable expert: a logit row holds NaN, "
+                                       "which means the router input upstream is bad, not the top-k");
+    return fail(SP_MOE_ECUDA, "gemma4-MoE: kernel error word %d", st);
+}
+
+extern "C" int sp_moe_forward(sp_moe *h, int lf, int nl, int flavour, int M,
+                              const float *x, float *y, int32_t *sel, float *wts) {
+    int rc = check_forward(h, lf, nl, flavour, M, x, y, "sp_moe_forward");
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    const size_t nx = (size_t)M * h->cfg.E * 4, ns = (size_t)nl * M * h->cfg.NU * 4;
+    CK(cudaMemcpyAsync(h->x_dev, x, nx, cudaMemcpyHostToDevice, h->stream), "x H2D");
+    rc = sp_moe_forward_dev(h, lf, nl, flavour, M, h->x_dev, h->y_dev, sel ? h->sel_dev : nullptr, wts ? h->wts_dev : nullptr, h->stream);
+    if (rc) return rc;
+    CK(cudaMemcpyAsync(y, h->y_dev, nx, cudaMemcpyDeviceToHost, h->stream), "y D2H");
+    if (sel) CK(cudaMemcpyAsync(sel, h->sel_dev, ns, cudaMemcpyDeviceToHost, h->stream), "sel D2H");
+    if (wts) CK(cudaMemcpyAsync(wts, h->wts_dev, ns, cudaMemcpyDeviceToHost, h->stream), "wts D2H");
+    return sp_moe_status(h);
+}

@@ -1,0 +1,132 @@
+"""Host-side mirror of the reference's MoE feed-forward seam, over the C ABI.
+
+`MoeEngine.forward` is g4_ffn_block -> g4_ffn_apply(moe_on=1) of the reference
+(src/backends/cuda/cuda_forward.cu:9101-9114, 8314-9050): x [M][E] in, updated residual out,
+for a run of consecutive layers. Weights are passed per layer in the reference's own layouts
+(include/sp_engine/sp_model.h:50-53). torch is used only to own device buffers and streams.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import SpMoeConfig, SpMoeLayerWeights, check
+
+FLAVOUR_DECODE = 0     # int8 activation quant + exact integer dots (reference decode arithmetic)
+FLAVOUR_PREFILL = 1    # exact Q4B dequant + floating-point GEMM (reference prefill arithmetic)
+
+GEMMA4_26B_A4B = dict(E=2816, NE=128, NU=8, FFE=704, FFS=2112, eps=1e-6)
+
+WEIGHT_FIELDS = _lib._PTR_FIELDS
+
+
+def _ptr(a):
+    """Address of a numpy array (host) or torch tensor (device)."""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        if not a.flags["C_CONTIGUOUS"]:
+            raise ValueError("weight arrays must be C-contiguous")
+        return a.ctypes.data
+    return a.data_ptr()
+
+
+class MoeEngine:
+    """Owns one sp_moe handle: the resident arena of every layer's experts plus scratch."""
+
+    def __init__(self, E, NE, NU, FFE, FFS, n_layers, max_tokens=1, eps=1e-6, device=0):
+        self.cfg = dict(E=E, NE=NE, NU=NU, FFE=FFE, FFS=FFS, eps=eps)
+        self.n_layers, self.max_tokens, self.device = n_layers, max_tokens, device
+        c = SpMoeConfig(E=E, NE=NE, NU=NU, FFE=FFE, FFS=FFS, n_layers=n_layers,
+                        max_tokens=max_tokens, device=device, eps=eps)
+        self._h = C.c_void_p()
+        check(_lib.lib().sp_moe_open(C.byref(c), C.byref(self._h)))
+
+    # -- lifecycle
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().sp_moe_close(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def device_bytes(self):
+        return _lib.lib().sp_moe_device_bytes(self._h)
+
+    @property
+    def kernel_launches(self):
+        return _lib.lib().sp_moe_kernel_launches(self._h)
+
+    # -- weights
+    def upload_layer(self, layer, weights, on_device=False):
+        """weights: mapping or object with the fields of sp_moe_layer_weights (numpy arrays, or
+        torch CUDA tensors when on_device)."""
+        get = weights.get if isinstance(weights, dict) else (lambda k: getattr(weights, k, None))
+        keep = [get(f) for f in WEIGHT_FIELDS]
+        w = SpMoeLayerWeights(*[_ptr(a) for a in keep])
+        fn = _lib.lib().sp_moe_upload_layer_dev if on_device else _lib.lib().sp_moe_upload_layer
+        check(fn(self._h, layer, C.byref(w)))
+
+    # -- forward
+    def forward(self, x, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, want_routing=True):
+        """Host entry: x numpy [M][E] f32 -> (y, sel, wts); sel/wts are [n_layers][M][NU]."""
+        n_layers = self.n_layers - layer_first if n_layers is None else n_layers
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.cfg["E"])
+        M = x.shape[0]
+        y = np.empty_like(x)
+        sel = np.empty((n_layers, M, self.cfg["NU"]), np.int32) if want_routing else None
+        wts = np.empty((n_layers, M, self.cfg["NU"]), np.float32) if want_routing else None
+        check(_lib.lib().sp_moe_forward(self._h, layer_first, n_layers, flavour, M, _ptr(x), _ptr(y),
+                                        _ptr(sel), _ptr(wts)))
+        return y, sel, wts
+
+    def forward_dev(self, x, y, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, sel=None, wts=None, stream=None):
+        """Device entry: x, y torch CUDA f32 [M][E]; enqueues on `stream` (a torch stream; default
+        the current one) and returns at once. Call status() to collect kernel-side errors."""
+        import torch
+        n_layers = self.n_layers - layer_first if n_layers is None else n_layers
+        M = x.numel() // self.cfg["E"]
+        st = (stream or torch.cuda.current_stream(x.device)).cuda_stream
+        check(_lib.lib().sp_moe_forward_dev(self._h, layer_first, n_layers, flavour, M, x.data_ptr(), y.data_ptr(),
+                                            _ptr(sel), _ptr(wts), st))
+
+    def status(self):
+        check(_lib.lib().sp_moe_status(self._h))
+
+
+def q4b_quantize(w):
+    """torch CUDA f32 [rows][cols] -> (codes uint8 [rows][cols/2], scales int16-view f16 [rows][cols/32])."""
+    import torch
+    rows, cols = w.shape
+    w = w.contiguous()
+    codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=w.device)
+    bs = torch.empty((rows, cols // 32), dtype=torch.int16, device=w.device)
+    check(_lib.lib().sp_moe_q4b_quantize_dev(w.data_ptr(), rows, cols, codes.data_ptr(), bs.data_ptr(),
+                                             torch.cuda.current_stream(w.device).cuda_stream))
+    return codes, bs
+
+
+def q4b_dequantize(codes, bs):
+    import torch
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    w = torch.empty((rows, cols), dtype=torch.float32, device=codes.device)
+    check(_lib.lib().sp_moe_q4b_dequantize_dev(codes.data_ptr(), bs.data_ptr(), rows, cols, w.data_ptr(),
+                                               torch.cuda.current_stream(codes.device).cuda_stream))
+    return w
+
+
+def gelu_mul(g, up):
+    """torch CUDA f32 tensors -> gelu_tanh(g) * up (k_gelu_mul of the reference)."""
+    import torch
+    g, up = g.contiguous(), up.contiguous()
+    out = torch.empty_like(g)
+    check(_lib.lib().sp_moe_gelu_mul_dev(g.data_ptr(), up.data_ptr(), g.numel(), out.data_ptr(),
+                                         torch.cuda.current_stream(g.device).cuda_stream))
+    return out
