@@ -54,10 +54,11 @@ struct sp_moe {
     std::vector<SpLayerDev> layers_host;
     std::vector<unsigned char> has_bias, uploaded;
     /* decode scratch */
-    float *logits, *hd, *dn, *hbuf, *acc;
-    unsigned *bar; int *status;
-    unsigned bar_epoch;
-    int dec_grid; size_t dec_smem;
+    unsigned long long *xch;    /* exchange words: logits | hd | dn | h | acc */
+    size_t xch_words;
+    int *status;
+    unsigned epoch;
+    int dec_grid, dec_slots; size_t dec_smem;
     /* host-pointer entry staging */
     float *x_dev, *y_dev; int32_t *sel_dev; float *wts_dev;
     SpBatchedScratch bs;
@@ -136,11 +137,11 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     OPEN_CK(cudaMemcpy(h->layers_dev, h->layers_host.data(), sizeof(SpLayerDev) * c.n_layers, cudaMemcpyHostToDevice), "layer table H2D");
     size_t sb = 0;
     auto dalloc = [&](void **p, size_t bytes) { sb += up256(bytes); return cudaMalloc(p, bytes); };
-    OPEN_CK(dalloc((void **)&h->logits, 4 * (size_t)c.NE), "scratch"); OPEN_CK(dalloc((void **)&h->hd, 4 * (size_t)c.FFS), "scratch");
-    OPEN_CK(dalloc((void **)&h->dn, 4 * (size_t)c.E), "scratch"); OPEN_CK(dalloc((void **)&h->hbuf, 4 * (size_t)c.NU * c.FFE), "scratch");
-    OPEN_CK(dalloc((void **)&h->acc, 4 * (size_t)c.E), "scratch");
-    OPEN_CK(dalloc((void **)&h->bar, 256), "scratch"); OPEN_CK(dalloc((void **)&h->status, 256), "scratch");
-    OPEN_CK(cudaMemset(h->bar, 0, 256), "memset"); OPEN_CK(cudaMemset(h->status, 0, 256), "memset");
+    h->xch_words = (size_t)c.NE + c.FFS + c.E + (size_t)c.NU * c.FFE + c.E;
+    OPEN_CK(dalloc((void **)&h->xch, 8 * h->xch_words), "scratch");
+    OPEN_CK(cudaMemset(h->xch, 0, 8 * h->xch_words), "memset");
+    OPEN_CK(dalloc((void **)&h->status, 256), "scratch");
+    OPEN_CK(cudaMemset(h->status, 0, 256), "memset");
     const size_t mt = (size_t)c.max_tokens;
     OPEN_CK(dalloc((void **)&h->x_dev, 4 * mt * c.E), "staging"); OPEN_CK(dalloc((void **)&h->y_dev, 4 * mt * c.E), "staging");
     OPEN_CK(dalloc((void **)&h->sel_dev, 4 * mt * c.NU * c.n_layers), "staging"); OPEN_CK(dalloc((void **)&h->wts_dev, 4 * mt * c.NU * c.n_layers), "staging");
@@ -150,8 +151,11 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     h->scratch_bytes = sb;
     /* persistent decode kernel: one CTA per SM, co-resident */
     {
-        int sms = 0; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
-        h->dec_smem = sp_decode_smem_bytes(h->d, sms);
+        int sms = 0, optin = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
+        h->dec_slots = sp_decode_slots(h->d, sms, (size_t)optin, &h->dec_smem);
+        if (h->dec_slots < 2) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM's shared memory (%d B)", optin); }
         int grid = 0;
         OPEN_CK(sp_decode_prepare(h->dec_smem, &grid), "decode kernel attributes");
         if (grid <= 0) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM (%zu B shared memory)", h->dec_smem); }
@@ -167,7 +171,7 @@ extern "C" int sp_moe_close(sp_moe *h) {
     cudaSetDevice(h->device);
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
     sp_batched_free(&h->bs);
-    void *ps[] = {h->arena, h->layers_dev, h->logits, h->hd, h->dn, h->hbuf, h->acc, h->bar, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
+    void *ps[] = {h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
     for (void *p : ps) if (p) cudaFree(p);
     cudaGetLastError();
     delete h;
@@ -228,9 +232,15 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
         SpDecodeArgs a;
         a.layers = h->layers_dev; a.layer_first = lf; a.n_layers = nl; a.d = h->d;
         a.x_in = x_dev; a.y_out = y_dev; a.sel_out = sel_dev; a.wts_out = wts_dev;
-        a.logits = h->logits; a.hd = h->hd; a.dn = h->dn; a.h = h->hbuf; a.acc = h->acc;
-        a.bar = h->bar; a.status = h->status; a.bar_base = h->bar_epoch;
-        h->bar_epoch += (unsigned)(h->dec_grid * sp_decode_barriers_per_layer() * nl);
+        if (h->epoch > 0xFFFFFFFFu - (unsigned)nl - 2u) {      /* epoch wrap: start over on clean words */
+            CK(cudaMemsetAsync(h->xch, 0, 8 * h->xch_words, st), "memset");
+            h->epoch = 0;
+        }
+        unsigned long long *x = h->xch;
+        a.x_logits = x; x += h->cfg.NE; a.x_hd = x; x += h->cfg.FFS; a.x_dn = x; x += h->cfg.E;
+        a.x_h = x; x += (size_t)h->cfg.NU * h->cfg.FFE; a.x_acc = x;
+        a.status = h->status; a.epoch_base = h->epoch; a.n_slots = h->dec_slots;
+        h->epoch += (unsigned)nl;
         CK(sp_decode_launch(a, h->dec_grid, h->dec_smem, st), "decode kernel launch");
         h->launches += 1;
         return SP_MOE_OK;
@@ -250,9 +260,8 @@ extern "C" int sp_moe_status(sp_moe *h) {
     CK(cudaMemcpy(&st, h->status, sizeof st, cudaMemcpyDeviceToHost), "status D2H");
     if (st == SP_KERR_NONE) return SP_MOE_OK;
     cudaMemset(h->status, 0, sizeof(int));
-    if (st == SP_KERR_BARRIER_TIMEOUT) {            /* counters are no longer consistent: start over */
-        cudaMemset(h->bar, 0, 256); h->bar_epoch = 0;
-        return fail(SP_MOE_ECUDA, "gemma4-MoE: a grid barrier wait ran out; the step's output is invalid");
+    if (st == SP_KERR_BARRIER_TIMEOUT) {
+        return fail(SP_MOE_ECUDA, "gemma4-MoE: a bounded device-side wait ran out; the step's output is invalid");
     }
     if (st == SP_KERR_NAN_ROUTER)                     /* CF:8596-8620 */
         return fail(SP_MOE_EBADSTATE, "gemma4-MoE: router produced no usable expert: a logit row holds NaN, "

@@ -35,18 +35,18 @@ enum { SP_KERR_NONE = 0, SP_KERR_NAN_ROUTER = 1, SP_KERR_BARRIER_TIMEOUT = 2, SP
 /* streamed-once weight bytes: read-only path, do not keep in L1 */
 __device__ __forceinline__ int4 ld_stream16(const void *p) {
     int4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.s32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.L2::128B.v4.s32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 __device__ __forceinline__ unsigned short ld_stream_u16(const void *p) {
     unsigned short v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    asm("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
 }
 __device__ __forceinline__ float4 ld_stream_f4(const void *p) {
     float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.f32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.L2::128B.v4.f32 {%0,%1,%2,%3}, [%4];"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
 }
@@ -156,6 +156,28 @@ __device__ __forceinline__ float quant_block16(const float *v, signed char *dst,
     }
     *corr = 8 * s;
     return scale;
+}
+
+/* Same quantiser, one element per thread: the 16 lanes of a half-warp hold one block. Every
+ * lane of the warp must call (shuffles use the full mask); `valid` gates only the stores.
+ * dst/sx/corr point at the block's own slots. */
+__device__ __forceinline__ void quant_elem16(float v, bool valid, signed char *dst_block, float *sx_b, int *corr_b) {
+    const int k = threadIdx.x & 15;
+    float m = fabsf(v);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float scale = m > 0.0f ? __fmul_rn(m, 1.0f / 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    int q = __float2int_rn(__fmul_rn(v, inv));
+    q = q > 127 ? 127 : q; q = q < -127 ? -127 : q;
+    int s = q;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (valid) {
+        const int r = k & 7;
+        dst_block[(k & 8) + ((r & 1) << 2) + (r >> 1)] = (signed char)q;
+        if (k == 0) { *sx_b = scale; *corr_b = 8 * s; }
+    }
 }
 
 /* ---------------------------------------------------------------- block-wide f64 sum of squares (CF:497-514)

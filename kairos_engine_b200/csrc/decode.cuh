@@ -10,19 +10,20 @@ struct SpDecodeArgs {
     float *y_out;                  /* [E] */
     int32_t *sel_out;              /* [n_layers][NU] descending-p ids, or NULL */
     float *wts_out;                /* [n_layers][NU], or NULL */
-    /* scratch in device memory, written by some CTAs and read by others */
-    float *logits;                 /* [NE] */
-    float *hd;                     /* [FFS]      shared-expert GeGLU output */
-    float *dn;                     /* [E]        shared-expert down output */
-    float *h;                      /* [NU][FFE]  routed GeGLU outputs, ascending-id slots */
-    float *acc;                    /* [E]        combined routed output */
-    unsigned *bar;                 /* monotonically increasing arrival counter */
+    /* exchange buffers in device memory: 8-byte {f32 value, u32 epoch} words, written by the
+     * CTA that owns the element and polled by every CTA; zero-initialised, epochs start at 1 */
+    unsigned long long *x_logits;  /* [NE] */
+    unsigned long long *x_hd;      /* [FFS]      shared-expert GeGLU output */
+    unsigned long long *x_dn;      /* [E]        shared-expert down output */
+    unsigned long long *x_h;       /* [NU][FFE]  routed GeGLU outputs, ascending-id slots */
+    unsigned long long *x_acc;     /* [E]        combined routed output */
     int *status;                   /* SP_KERR_* */
-    unsigned bar_base;             /* counter value when this launch starts */
+    unsigned epoch_base;           /* layer li of this launch publishes epoch_base + li + 1 */
+    int n_slots;                   /* ring slots that fit the dynamic shared memory */
 };
 
-size_t sp_decode_smem_bytes(const SpDims &d, int grid);
+/* ring slots and total dynamic shared memory for these dims under `smem_limit`; 0 if it cannot fit */
+int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_bytes);
 int sp_decode_threads();
-int sp_decode_barriers_per_layer();
 cudaError_t sp_decode_prepare(size_t smem, int *max_grid);
 cudaError_t sp_decode_launch(const SpDecodeArgs &args, int grid, size_t smem, cudaStream_t st);
