@@ -157,7 +157,7 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         h->dec_slots = sp_decode_slots(h->d, sms, (size_t)optin, &h->dec_smem);
         if (h->dec_slots < 2) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM's shared memory (%d B)", optin); }
         int grid = 0;
-        OPEN_CK(sp_decode_prepare(h->dec_smem, &grid), "decode kernel attributes");
+        OPEN_CK(sp_decode_prepare(h->d, h->dec_smem, &grid), "decode kernel attributes");
         if (grid <= 0) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM (%zu B shared memory)", h->dec_smem); }
         h->dec_grid = grid;
     }
@@ -229,10 +229,19 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
     cudaStream_t st = (cudaStream_t)stream;
     h->last_stream = st;
     if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
+        /* at most 64 layers per launch (the bias mask is one word): longer runs chain launches */
+        const float *xin = x_dev;
+        for (int l0 = lf; l0 < lf + nl; l0 += 64) {
+        const int cnt = (lf + nl - l0) < 64 ? (lf + nl - l0) : 64;
         SpDecodeArgs a;
-        a.layers = h->layers_dev; a.layer_first = lf; a.n_layers = nl; a.d = h->d;
-        a.x_in = x_dev; a.y_out = y_dev; a.sel_out = sel_dev; a.wts_out = wts_dev;
-        if (h->epoch > 0xFFFFFFFFu - (unsigned)nl - 2u) {      /* epoch wrap: start over on clean words */
+        a.layer0 = layer_view(h, 0, true); a.layer_stride = h->layer_bytes; a.bias_mask = 0;
+        for (int i = 0; i < cnt; i++) if (h->has_bias[l0 + i]) a.bias_mask |= 1ull << i;
+        a.layer_first = l0; a.n_layers = cnt; a.d = h->d;
+        a.x_in = xin; a.y_out = y_dev;
+        a.sel_out = sel_dev ? sel_dev + (size_t)(l0 - lf) * h->cfg.NU : nullptr;
+        a.wts_out = wts_dev ? wts_dev + (size_t)(l0 - lf) * h->cfg.NU : nullptr;
+        const int nl_launch = cnt;
+        if (h->epoch > 0xFFFFFFFFu - (unsigned)nl_launch - 2u) {      /* epoch wrap: start over on clean words */
             CK(cudaMemsetAsync(h->xch, 0, 8 * h->xch_words, st), "memset");
             h->epoch = 0;
         }
@@ -240,13 +249,15 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
         a.x_logits = x; x += h->cfg.NE; a.x_hd = x; x += h->cfg.FFS; a.x_dn = x; x += h->cfg.E;
         a.x_h = x; x += (size_t)h->cfg.NU * h->cfg.FFE; a.x_acc = x;
         a.status = h->status; a.epoch_base = h->epoch; a.n_slots = h->dec_slots;
-        h->epoch += (unsigned)nl;
+        h->epoch += (unsigned)nl_launch;
         CK(sp_decode_launch(a, h->dec_grid, h->dec_smem, st), "decode kernel launch");
         h->launches += 1;
+        xin = y_dev;
+        }
         return SP_MOE_OK;
     }
     int nlaunch = 0;
-    cudaError_t e = sp_batched_forward(h->d, h->layers_dev, lf, nl, flavour, M, x_dev, y_dev, sel_dev, wts_dev, &h->bs, h->status, st, &nlaunch);
+    cudaError_t e = sp_batched_forward(h->d, h->layers_host.data(), lf, nl, flavour, M, x_dev, y_dev, sel_dev, wts_dev, &h->bs, h->status, st, &nlaunch);
     h->launches += (uint64_t)nlaunch;
     if (e != cudaSuccess) return fail_cuda(e, "batched forward launch");
     return SP_MOE_OK;

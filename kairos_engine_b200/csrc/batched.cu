@@ -1,6 +1,439 @@
-/* batched.cu — placeholder until the M > 1 kernels land: reports "not supported". */
+/* batched.cu — the M > 1 paths of the MoE feed-forward layer: a few stream-ordered kernels per
+ * layer with routing, bucketing and combine all on the device (no host round trip).
+ *
+ * Replaces g4_ffn_apply's expert-major batched branch (CF:8430-8965 of
+ * src/backends/cuda/cuda_forward.cu): batched router prep + router GEMM, the D2H + host top-k +
+ * host bucketing (CF:8483-8625), per-expert gather / GEMM / GELU split / GEMM / scatter-acc
+ * (CF:8925-8965), and the recombine (CF:9014-9019).
+ *
+ * Two arithmetic flavours, the reference's AMMD switch (CF:8322-8324):
+ *   decode  (per-token int8 activation quant + exact integer dots; what B sequential decode
+ *            steps compute, CF:11737-11757) for small batches;
+ *   prefill (w = code * f16 scale exactly, floating-point dot, fp32 accumulate; gemm_w,
+ *            CF:13488-13518) for large ones.
+ * Every (token, expert) pair is computed independently and the per-token combine walks the
+ * experts in ascending id with acc = acc + w*out, so results do not depend on scheduling.
+ */
 #include "batched.cuh"
-cudaError_t sp_batched_alloc(const SpDims &, int max_tokens, SpBatchedScratch *s, size_t *bytes) { s->base = nullptr; s->bytes = 0; s->max_tokens = max_tokens; *bytes = 0; return cudaSuccess; }
+#include "../../include/sp_engine/moe_backend.h"
+
+namespace {
+
+struct BView {                 /* carved scratch */
+    float *rin, *nx_f, *in_f, *logits, *cw, *hd, *dn, *h, *eo, *xa, *xb;
+    signed char *nx_q, *in_q, *hd_q, *h_q;
+    float *nx_s, *in_s, *hd_s, *h_s;
+    int *nx_c, *in_c, *hd_c, *h_c;
+    int *sel_asc, *count, *list;
+};
+
+size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+template <class F>
+size_t blayout(const SpDims &d, int Mx, F place) {
+    size_t o = 0; int id = 0;
+    auto take = [&](size_t bytes) { place(id++, o); o = up256(o + bytes); };
+    const size_t M = Mx, E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
+    take(4 * M * E); take(4 * M * E); take(4 * M * E); take(4 * M * NE); take(4 * M * NU);            /* rin nx_f in_f logits cw */
+    take(4 * M * FFS); take(4 * M * E); take(4 * M * NU * FFE); take(4 * M * NU * E);                /* hd dn h eo */
+    take(4 * M * E); take(4 * M * E);                                                               /* xa xb */
+    take(M * E); take(M * E); take(M * FFS); take(M * NU * FFE);                                     /* q */
+    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* s */
+    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* c */
+    take(4 * M * NU); take(4 * NE); take(4 * NE * M);                                               /* sel_asc count list */
+    return o;
+}
+BView bview(const SpDims &d, const SpBatchedScratch *s) {
+    unsigned char *p[26];
+    blayout(d, s->max_tokens, [&](int id, size_t off) { p[id] = (unsigned char *)s->base + off; });
+    BView v;
+    v.rin = (float *)p[0]; v.nx_f = (float *)p[1]; v.in_f = (float *)p[2]; v.logits = (float *)p[3]; v.cw = (float *)p[4];
+    v.hd = (float *)p[5]; v.dn = (float *)p[6]; v.h = (float *)p[7]; v.eo = (float *)p[8]; v.xa = (float *)p[9]; v.xb = (float *)p[10];
+    v.nx_q = (signed char *)p[11]; v.in_q = (signed char *)p[12]; v.hd_q = (signed char *)p[13]; v.h_q = (signed char *)p[14];
+    v.nx_s = (float *)p[15]; v.in_s = (float *)p[16]; v.hd_s = (float *)p[17]; v.h_s = (float *)p[18];
+    v.nx_c = (int *)p[19]; v.in_c = (int *)p[20]; v.hd_c = (int *)p[21]; v.h_c = (int *)p[22];
+    v.sel_asc = (int *)p[23]; v.count = (int *)p[24]; v.list = (int *)p[25];
+    return v;
+}
+
+/* ---------------------------------------------------------------- device helpers */
+/* sum of squares in the reference's order (k_rmsnorm, CF:503-511); blockDim.x == 256 */
+__device__ double sumsq256(const float *v, int n, double *sh) {
+    const int t = threadIdx.x;
+    double s = 0.0;
+    for (int i = t; i < n; i += 256) { const double a = v[i]; s += a * a; }
+    sh[t] = s;
+    __syncthreads();
+    for (int o = 128; o >= 32; o >>= 1) { if (t < o) sh[t] += sh[t + o]; __syncthreads(); }
+    if (t < 32) {
+        double a = sh[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_down_sync(0xffffffffu, a, o);
+        if (t == 0) sh[0] = a;
+    }
+    __syncthreads();
+    const double r = sh[0];
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float rms_scale_from(double ss, int n, float eps) {
+    const float ms = (float)(ss / (double)n);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
+}
+__device__ __forceinline__ float warp_tree(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    return v;
+}
+/* quantise one row with all 256 threads (k_quant_act_int8_batched, CF:1725-1746) */
+template <class F>
+__device__ __forceinline__ void quant_row(int n, signed char *q, float *sx, int *corr, F get) {
+    for (int base = 0; base < n; base += 256) {
+        const int i = base + (int)threadIdx.x;
+        const bool valid = i < n;
+        const float v = valid ? get(i) : 0.0f;
+        const int b = i >> 4;
+        quant_elem16(v, valid, q + 16 * b, sx + b, corr + b);
+    }
+}
+
+/* ---------------------------------------------------------------- K1: per-token norms of x (CF:8347, 8402-8404, 8425) */
+template <bool FA>
+__global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const float *x, BView v) {
+    __shared__ double sh[256];
+    const int t = blockIdx.x, E = d.E;
+    const float *xt = x + (size_t)t * E;
+    if (t == 0) for (int i = threadIdx.x; i < d.NE; i += 256) v.count[i] = 0;
+    const float scale = rms_scale_from(sumsq256(xt, E, sh), E, d.eps);
+    if (FA) {
+        const size_t b16 = (size_t)t * (E / 16);
+        quant_row(E, v.nx_q + (size_t)t * E, v.nx_s + b16, v.nx_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.ffn_norm + i)); });
+        quant_row(E, v.in_q + (size_t)t * E, v.in_s + b16, v.in_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i)); });
+    } else {
+        for (int i = threadIdx.x; i < E; i += 256) {
+            const float xs = __fmul_rn(xt[i], scale);
+            v.nx_f[(size_t)t * E + i] = __fmul_rn(xs, __ldg(L.ffn_norm + i));
+            v.in_f[(size_t)t * E + i] = __fmul_rn(xs, __ldg(L.pre_ffw2 + i));
+        }
+    }
+    for (int i = threadIdx.x; i < E; i += 256)
+        v.rin[(size_t)t * E + i] = __fmul_rn(__fmul_rn(__fmul_rn(xt[i], scale), d.inv_sqrt_e), __ldg(L.router_scale + i));
+}
+
+/* ---------------------------------------------------------------- K2: router logits, fp32, fixed order
+ * lane l takes the float4 groups q = l, l+32, ... with acc = fma(w, x, acc) over the four
+ * elements in order, then the shuffle tree (the same order the decode kernel uses). One block =
+ * 8 experts (one per warp) x TT tokens; the 8 router rows sit in shared memory. */
+constexpr int kRouterTT = 16;
+__global__ void __launch_bounds__(256) k_b_router(SpDims d, SpLayerDev L, BView v, int M) {
+    extern __shared__ __align__(16) float wsm[];              /* [8][E] */
+    const int E = d.E, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp, t0 = blockIdx.y * kRouterTT;
+    for (int i = threadIdx.x; i < 8 * (E >> 2); i += 256) {
+        const int r = i / (E >> 2), q = i - r * (E >> 2);
+        const int er = blockIdx.x * 8 + r;
+        reinterpret_cast<float4 *>(wsm)[i] = er < d.NE ? __ldg(reinterpret_cast<const float4 *>(L.router_w + (size_t)er * E) + q) : make_float4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    if (e >= d.NE) return;
+    const float *wrow = wsm + (size_t)warp * E;
+    const float bias = L.router_bias ? __ldg(L.router_bias + e) : 0.0f;
+    for (int t = t0; t < t0 + kRouterTT && t < M; t++) {
+        const float *rin = v.rin + (size_t)t * E;
+        float acc = 0.0f;
+        for (int q = lane; q < (E >> 2); q += 32) {
+            const float4 w = *reinterpret_cast<const float4 *>(wrow + 4 * q);
+            const float4 xv = __ldg(reinterpret_cast<const float4 *>(rin) + q);
+            acc = __fmaf_rn(w.x, xv.x, acc); acc = __fmaf_rn(w.y, xv.y, acc);
+            acc = __fmaf_rn(w.z, xv.z, acc); acc = __fmaf_rn(w.w, xv.w, acc);
+        }
+        acc = warp_tree(acc);
+        if (lane == 0) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(acc, bias) : acc;
+    }
+}
+
+/* ---------------------------------------------------------------- K3: moe_topk_host (CF:6220-6240) + bucketing by expert (CF:8594-8624) */
+__global__ void __launch_bounds__(256) k_b_topk(SpDims d, SpLayerDev L, BView v, int M, int32_t *sel_out, float *wts_out, int *status) {
+    extern __shared__ __align__(16) unsigned char tsm[];
+    const int NE = d.NE, NU = d.NU, t = threadIdx.x, tok = blockIdx.x;
+    double *ex = reinterpret_cast<double *>(tsm);               /* [NE] */
+    float *p = reinterpret_cast<float *>(ex + NE);              /* [NE] */
+    __shared__ double red[8];
+    __shared__ float wmax[8];
+    __shared__ int sel_desc[SP_MAX_NU];
+    __shared__ float p_desc[SP_MAX_NU];
+    const float *lg = v.logits + (size_t)tok * NE;
+    float mx = -INFINITY; int bad = 0;
+    for (int i = t; i < NE; i += 256) { const float l = lg[i]; if (l != l) bad = 1; mx = fmaxf(mx, l); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); bad |= __shfl_xor_sync(0xffffffffu, bad, o); }
+    if ((t & 31) == 0) wmax[t >> 5] = mx;
+    if (bad && (t & 31) == 0) atomicExch(status, SP_KERR_NAN_ROUTER);
+    __syncthreads();
+    mx = wmax[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) mx = fmaxf(mx, wmax[w]);
+    double part = 0.0;
+    for (int i = t; i < NE; i += 256) { const double e = exp((double)lg[i] - (double)mx); ex[i] = e; part += e; }
+    part = warp_sum_f64(part);
+    if ((t & 31) == 0) red[t >> 5] = part;
+    __syncthreads();
+    double sum = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) sum += red[w];
+    for (int i = t; i < NE; i += 256) p[i] = (float)(ex[i] / sum);
+    if (t < SP_MAX_NU) { sel_desc[t] = t < NE ? t : 0; p_desc[t] = 0.0f; }
+    __syncthreads();
+    for (int i = t; i < NE; i += 256) {
+        const float pi = p[i]; int r = 0;
+        for (int j = 0; j < NE; j++) { const float pj = p[j]; r += (pj > pi) || (pj == pi && j < i); }
+        if (r < NU && pi == pi) { sel_desc[r] = i; p_desc[r] = pi; }
+    }
+    __syncthreads();
+    if (t < NU) {
+        float wsum = 0.0f;
+        for (int k = 0; k < NU; k++) wsum = __fadd_rn(wsum, p_desc[k]);
+        if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
+        const int e = sel_desc[t];
+        const float w = __fdiv_rn(p_desc[t], wsum);
+        int slot = 0;
+        for (int j = 0; j < NU; j++) slot += (sel_desc[j] < e);
+        const int pair = tok * NU + slot;
+        v.sel_asc[pair] = e;
+        v.cw[pair] = __fmul_rn(w, __ldg(L.dexps_scale + e));             /* CF:8709 */
+        const int pos = atomicAdd(&v.count[e], 1);
+        if (pos < M) v.list[(size_t)e * M + pos] = pair; else atomicExch(status, SP_KERR_OVERFLOW);
+        if (sel_out) sel_out[(size_t)tok * NU + t] = e;
+        if (wts_out) wts_out[(size_t)tok * NU + t] = w;
+    }
+}
+
+/* ---------------------------------------------------------------- K5: per-row activation quant (CF:1725-1746) */
+__global__ void __launch_bounds__(256) k_b_quant_rows(const float *x, int n, signed char *q, float *sx, int *corr) {
+    const size_t r = blockIdx.x;
+    const float *xr = x + r * n;
+    quant_row(n, q + r * n, sx + r * (n / 16), corr + r * (n / 16), [&](int i) { return xr[i]; });
+}
+
+/* ---------------------------------------------------------------- K4/K6: Q4B rows x a list of activations
+ * One warp per output row (or gate/up row pair); its codes and block scales are loaded ONCE into
+ * registers and reused for every activation in the group's list, so each weight byte is read from
+ * HBM once per layer however many tokens share the expert. grid.y = group (expert, or 0 for the
+ * shared expert whose list is every token). */
+struct GroupArgs {
+    const uint8_t *codes; const uint16_t *bs;      /* tensor base */
+    long long rows_per_group;                      /* row stride between groups */
+    const int *count, *list; int list_stride;      /* per-group lists (NULL list = identity 0..M-1) */
+    int M, in, rows;                               /* rows (or pairs) per group */
+    int up_off;                                    /* PAIR: row offset of the up row */
+    const uint8_t *ucodes; const uint16_t *ubs;    /* PAIR with a separate up tensor (shared expert), else NULL */
+    int act_div;                                   /* activation row = item / act_div (NU for routed gate|up, 1 otherwise) */
+    /* flavour A */
+    const signed char *q; const float *sx; const int *corr;
+    /* flavour B */
+    const float *xf;
+    float *out; int out_stride;                    /* out[item * out_stride + row] */
+};
+
+template <int NIT>
+__device__ __forceinline__ void load_row(const uint8_t *codes, const uint16_t *bs, int n32, int lane, int4 (&w)[NIT], float (&sc)[NIT]) {
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int c = lane + 32 * i;
+        if (c < n32) { w[i] = ld_stream16(codes + 16 * (size_t)c); sc[i] = h2f(ld_stream_u16(bs + c)); }
+        else { w[i] = make_int4(0, 0, 0, 0); sc[i] = 0.0f; }
+    }
+}
+template <int NIT>
+__device__ __forceinline__ float dot_a(const int4 (&w)[NIT], const float (&sc)[NIT], int n32, int lane,
+                                       const int4 *q, const float *sx, const int *corr) {
+    float facc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int c = lane + 32 * i;
+        if (c < n32) {
+            const int2 cr = *reinterpret_cast<const int2 *>(corr + 2 * c);
+            const float2 s2 = *reinterpret_cast<const float2 *>(sx + 2 * c);
+            int a0, a1;
+            q4b_chunk_dot(w[i], q[2 * c], q[2 * c + 1], cr.x, cr.y, a0, a1);
+            facc = __fmaf_rn(sc[i], __fmaf_rn((float)a0, s2.x, __fmul_rn((float)a1, s2.y)), facc);
+        }
+    }
+    return warp_tree(facc);
+}
+/* flavour B: w = code * scale exactly (CF:1459-1463), fp32 dot */
+template <int NIT>
+__device__ __forceinline__ float dot_b(const int4 (&w)[NIT], const float (&sc)[NIT], int n32, int lane, const float *x) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int c = lane + 32 * i;
+        if (c < n32) {
+            const float4 *xv = reinterpret_cast<const float4 *>(x + 32 * c);
+            const int words[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+            float blk = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float4 x0 = xv[2 * k], x1 = xv[2 * k + 1];
+                const int wd = words[k];
+                blk = __fmaf_rn((float)(((wd & 0xF) ^ 8) - 8), x0.x, blk);
+                blk = __fmaf_rn((float)((((wd >> 4) & 0xF) ^ 8) - 8), x0.y, blk);
+                blk = __fmaf_rn((float)((((wd >> 8) & 0xF) ^ 8) - 8), x0.z, blk);
+                blk = __fmaf_rn((float)((((wd >> 12) & 0xF) ^ 8) - 8), x0.w, blk);
+                blk = __fmaf_rn((float)((((wd >> 16) & 0xF) ^ 8) - 8), x1.x, blk);
+                blk = __fmaf_rn((float)((((wd >> 20) & 0xF) ^ 8) - 8), x1.y, blk);
+                blk = __fmaf_rn((float)((((wd >> 24) & 0xF) ^ 8) - 8), x1.z, blk);
+                blk = __fmaf_rn((float)((((wd >> 28) & 0xF) ^ 8) - 8), x1.w, blk);
+            }
+            acc = __fmaf_rn(sc[i], blk, acc);
+        }
+    }
+    return warp_tree(acc);
+}
+
+template <bool FA, bool PAIR, int NIT>
+__global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = blockIdx.y;
+    const int cnt = g.count ? g.count[grp] : g.M;
+    if (cnt == 0) return;
+    const int r = blockIdx.x * 8 + warp;
+    if (r >= g.rows) return;
+    const int n32 = g.in >> 5;
+    const size_t rb = (size_t)g.in / 2;
+    const size_t row = (size_t)grp * g.rows_per_group + r;
+    int4 w0[NIT], w1[PAIR ? NIT : 1]; float s0[NIT], s1[PAIR ? NIT : 1];
+    load_row<NIT>(g.codes + row * rb, g.bs + row * n32, n32, lane, w0, s0);
+    if (PAIR) {
+        if (g.ucodes) load_row<NIT>(g.ucodes + row * rb, g.ubs + row * n32, n32, lane, reinterpret_cast<int4(&)[NIT]>(w1), reinterpret_cast<float(&)[NIT]>(s1));
+        else load_row<NIT>(g.codes + (row + g.up_off) * rb, g.bs + (row + g.up_off) * n32, n32, lane, reinterpret_cast<int4(&)[NIT]>(w1), reinterpret_cast<float(&)[NIT]>(s1));
+    }
+    const int *list = g.list ? g.list + (size_t)grp * g.list_stride : nullptr;
+    const int b16 = g.in >> 4;
+    for (int i = 0; i < cnt; i++) {
+        const int item = list ? list[i] : i;
+        const size_t arow = (size_t)(item / g.act_div);
+        float o;
+        if (FA) {
+            const int4 *q = reinterpret_cast<const int4 *>(g.q + arow * g.in);
+            const float *sx = g.sx + arow * b16; const int *corr = g.corr + arow * b16;
+            o = dot_a<NIT>(w0, s0, n32, lane, q, sx, corr);
+            if (PAIR) o = gelu_mul(o, dot_a<NIT>(reinterpret_cast<int4(&)[NIT]>(w1), reinterpret_cast<float(&)[NIT]>(s1), n32, lane, q, sx, corr));
+        } else {
+            const float *x = g.xf + arow * g.in;
+            o = dot_b<NIT>(w0, s0, n32, lane, x);
+            if (PAIR) o = gelu_mul(o, dot_b<NIT>(reinterpret_cast<int4(&)[NIT]>(w1), reinterpret_cast<float(&)[NIT]>(s1), n32, lane, x));
+        }
+        if (lane == 0) g.out[(size_t)item * g.out_stride + r] = o;
+    }
+}
+
+template <bool FA, bool PAIR>
+void launch_rows(const GroupArgs &g, int groups, cudaStream_t st, int *nl) {
+    const dim3 grid((unsigned)((g.rows + 7) / 8), (unsigned)groups);
+    const int nit = ((g.in >> 5) + 31) >> 5;
+    if (nit <= 1) k_b_rows<FA, PAIR, 1><<<grid, 256, 0, st>>>(g);
+    else if (nit == 2) k_b_rows<FA, PAIR, 2><<<grid, 256, 0, st>>>(g);
+    else if (nit == 3) k_b_rows<FA, PAIR, 3><<<grid, 256, 0, st>>>(g);
+    else k_b_rows<FA, PAIR, 4><<<grid, 256, 0, st>>>(g);
+    (*nl)++;
+}
+
+/* ---------------------------------------------------------------- K7: ordered combine + recombine (CF:6071-6077, 9014-9019) */
+__global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, float *y) {
+    extern __shared__ __align__(16) float fsm[];              /* [2][E] */
+    __shared__ double sh[256];
+    const int t = blockIdx.x, E = d.E, NU = d.NU;
+    float *va = fsm, *vb = fsm + E;
+    float cw[SP_MAX_NU];
+#pragma unroll
+    for (int k = 0; k < SP_MAX_NU; k++) cw[k] = k < NU ? v.cw[(size_t)t * NU + k] : 0.0f;
+    for (int i = threadIdx.x; i < E; i += 256) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int k = 0; k < SP_MAX_NU; k++) if (k < NU) acc = __fadd_rn(acc, __fmul_rn(cw[k], v.eo[((size_t)t * NU + k) * E + i]));
+        vb[i] = acc;
+        va[i] = v.dn[(size_t)t * E + i];
+    }
+    __syncthreads();
+    const float sc1 = rms_scale_from(sumsq256(va, E, sh), E, d.eps);
+    const float sc2 = rms_scale_from(sumsq256(vb, E, sh), E, d.eps);
+    for (int i = threadIdx.x; i < E; i += 256) {
+        const float mlp = __fmul_rn(__fmul_rn(va[i], sc1), __ldg(L.post_ffw1 + i));
+        const float t1 = __fmul_rn(__fmul_rn(vb[i], sc2), __ldg(L.post_ffw2 + i));
+        va[i] = __fadd_rn(mlp, t1);
+    }
+    __syncthreads();
+    const float sc3 = rms_scale_from(sumsq256(va, E, sh), E, d.eps);
+    for (int i = threadIdx.x; i < E; i += 256)
+        y[(size_t)t * E + i] = __fadd_rn(x[(size_t)t * E + i], __fmul_rn(__fmul_rn(va[i], sc3), __ldg(L.post_ffw + i)));
+}
+
+template <bool FA>
+cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *x, float *y, int32_t *sel, float *wts,
+                      BView &v, int *status, cudaStream_t st, int *nl) {
+    const int E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
+    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v); (*nl)++;
+    {
+        const size_t sm = (size_t)8 * E * 4;
+        cudaError_t e = cudaFuncSetAttribute(k_b_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return e;
+        k_b_router<<<dim3((NE + 7) / 8, (M + kRouterTT - 1) / kRouterTT), 256, sm, st>>>(d, L, v, M); (*nl)++;
+    }
+    k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
+    GroupArgs g{};
+    g.M = M;
+    /* shared expert gate/up -> hd (CF:8348-8356) */
+    g.codes = L.sg_codes; g.bs = L.sg_bs; g.ucodes = L.su_codes; g.ubs = L.su_bs; g.rows_per_group = 0; g.count = nullptr; g.list = nullptr;
+    g.in = E; g.rows = FFS; g.up_off = 0; g.act_div = 1; g.q = v.nx_q; g.sx = v.nx_s; g.corr = v.nx_c; g.xf = v.nx_f; g.out = v.hd; g.out_stride = FFS;
+    launch_rows<FA, true>(g, 1, st, nl);
+    /* routed gate|up -> h (CF:8733-8737, 8958-8959) */
+    g.codes = L.gu_codes; g.bs = L.gu_bs; g.ucodes = nullptr; g.ubs = nullptr; g.rows_per_group = 2LL * FFE; g.count = v.count; g.list = v.list; g.list_stride = M;
+    g.in = E; g.rows = FFE; g.up_off = FFE; g.act_div = NU; g.q = v.in_q; g.sx = v.in_s; g.corr = v.in_c; g.xf = v.in_f; g.out = v.h; g.out_stride = FFE;
+    launch_rows<FA, true>(g, NE, st, nl);
+    if (FA) {
+        k_b_quant_rows<<<M, 256, 0, st>>>(v.hd, FFS, v.hd_q, v.hd_s, v.hd_c); (*nl)++;
+        k_b_quant_rows<<<M * NU, 256, 0, st>>>(v.h, FFE, v.h_q, v.h_s, v.h_c); (*nl)++;
+    }
+    /* shared down -> dn (CF:8358) */
+    g.codes = L.sd_codes; g.bs = L.sd_bs; g.rows_per_group = 0; g.count = nullptr; g.list = nullptr;
+    g.in = FFS; g.rows = E; g.act_div = 1; g.q = v.hd_q; g.sx = v.hd_s; g.corr = v.hd_c; g.xf = v.hd; g.out = v.dn; g.out_stride = E;
+    launch_rows<FA, false>(g, 1, st, nl);
+    /* routed down -> eo (CF:8739-8742, 8961) */
+    g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E; g.count = v.count; g.list = v.list; g.list_stride = M;
+    g.in = FFE; g.rows = E; g.act_div = 1; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = v.eo; g.out_stride = E;
+    launch_rows<FA, false>(g, NE, st, nl);
+    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, y); (*nl)++;
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *s, size_t *bytes) {
+    s->base = nullptr; s->bytes = 0; s->max_tokens = max_tokens; *bytes = 0;
+    s->bytes = blayout(d, max_tokens, [](int, size_t) {});
+    const cudaError_t e = cudaMalloc(&s->base, s->bytes);
+    if (e == cudaSuccess) *bytes = s->bytes; else s->base = nullptr;
+    return e;
+}
 void sp_batched_free(SpBatchedScratch *s) { if (s && s->base) cudaFree(s->base); if (s) s->base = nullptr; }
-cudaError_t sp_batched_forward(const SpDims &, const SpLayerDev *, int, int, int, int, const float *, float *, int32_t *, float *,
-                               SpBatchedScratch *, int *, cudaStream_t, int *nlaunch) { *nlaunch = 0; return cudaErrorNotSupported; }
+
+cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl_, int flavour, int M,
+                               const float *x, float *y, int32_t *sel, float *wts,
+                               SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+    *nlaunch = 0;
+    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
+    BView v = bview(d, s);
+    const float *cur = x;
+    for (int li = 0; li < nl_; li++) {
+        float *dst = (li == nl_ - 1) ? y : ((li & 1) ? v.xb : v.xa);
+        int32_t *sl = sel ? sel + (size_t)li * M * d.NU : nullptr;
+        float *wl = wts ? wts + (size_t)li * M * d.NU : nullptr;
+        const cudaError_t e = (flavour == SP_MOE_FLAVOUR_DECODE)
+            ? run_layer<true>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, status, st, nlaunch)
+            : run_layer<false>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, status, st, nlaunch);
+        if (e != cudaSuccess) return e;
+        cur = dst;
+    }
+    return cudaSuccess;
+}

@@ -71,13 +71,15 @@ __device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
 /* w: 16 B of codes; q: 32 de-interleaved int8 as two int4 (first 16 weights, last 16 weights) */
 __device__ __forceinline__ void q4b_chunk_dot(const int4 &w, const int4 &qa, const int4 &qb,
                                               int corr0, int corr1, int &a0, int &a1) {
-    unsigned t;
-    int s0 = 0, s1 = 0;
-    t = (unsigned)w.x ^ 0x88888888u; s0 = dp4a_us(t & 0x0F0F0F0Fu, qa.x, s0); s0 = dp4a_us((t >> 4) & 0x0F0F0F0Fu, qa.y, s0);
-    t = (unsigned)w.y ^ 0x88888888u; s0 = dp4a_us(t & 0x0F0F0F0Fu, qa.z, s0); s0 = dp4a_us((t >> 4) & 0x0F0F0F0Fu, qa.w, s0);
-    t = (unsigned)w.z ^ 0x88888888u; s1 = dp4a_us(t & 0x0F0F0F0Fu, qb.x, s1); s1 = dp4a_us((t >> 4) & 0x0F0F0F0Fu, qb.y, s1);
-    t = (unsigned)w.w ^ 0x88888888u; s1 = dp4a_us(t & 0x0F0F0F0Fu, qb.z, s1); s1 = dp4a_us((t >> 4) & 0x0F0F0F0Fu, qb.w, s1);
-    a0 = s0 - corr0; a1 = s1 - corr1;
+    /* low nibbles: (t & 0x0F0F0F0F) = code + 8; high nibbles are taken in place,
+     * (t & 0xF0F0F0F0) = 16 * (code + 8), and the exact factor 16 is shifted out of the sum */
+    const unsigned t0 = (unsigned)w.x ^ 0x88888888u, t1 = (unsigned)w.y ^ 0x88888888u;
+    const unsigned t2 = (unsigned)w.z ^ 0x88888888u, t3 = (unsigned)w.w ^ 0x88888888u;
+    const int l0 = dp4a_us(t1 & 0x0F0F0F0Fu, qa.z, dp4a_us(t0 & 0x0F0F0F0Fu, qa.x, -corr0));
+    const int h0 = dp4a_us(t1 & 0xF0F0F0F0u, qa.w, dp4a_us(t0 & 0xF0F0F0F0u, qa.y, 0));
+    const int l1 = dp4a_us(t3 & 0x0F0F0F0Fu, qb.z, dp4a_us(t2 & 0x0F0F0F0Fu, qb.x, -corr1));
+    const int h1 = dp4a_us(t3 & 0xF0F0F0F0u, qb.w, dp4a_us(t2 & 0xF0F0F0F0u, qb.y, 0));
+    a0 = l0 + (h0 >> 4); a1 = l1 + (h1 >> 4);
 }
 
 /* ---------------------------------------------------------------- tanhf, bit-reproducible
@@ -156,6 +158,36 @@ __device__ __forceinline__ float quant_block16(const float *v, signed char *dst,
     }
     *corr = 8 * s;
     return scale;
+}
+
+/* Same quantiser for a block held in registers, stored with one 16-byte write. */
+__device__ __forceinline__ void quant_block16_store(const float (&v)[16], int4 *dst, float *sx, int *corr) {
+    float a[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) a[i] = fabsf(v[i]);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < o; i++) a[i] = fmaxf(a[i], a[i + o]);
+    const float m = a[0];
+    const float scale = m > 0.0f ? __fmul_rn(m, 1.0f / 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    int q[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        int t = __float2int_rn(__fmul_rn(v[i], inv));
+        t = t > 127 ? 127 : t; t = t < -127 ? -127 : t;
+        q[i] = t;
+    }
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) s += q[i];
+    int4 w;
+    w.x = (q[0] & 0xFF) | ((q[2] & 0xFF) << 8) | ((q[4] & 0xFF) << 16) | ((q[6] & 0xFF) << 24);
+    w.y = (q[1] & 0xFF) | ((q[3] & 0xFF) << 8) | ((q[5] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+    w.z = (q[8] & 0xFF) | ((q[10] & 0xFF) << 8) | ((q[12] & 0xFF) << 16) | ((q[14] & 0xFF) << 24);
+    w.w = (q[9] & 0xFF) | ((q[11] & 0xFF) << 8) | ((q[13] & 0xFF) << 16) | ((q[15] & 0xFF) << 24);
+    *dst = w; *sx = scale; *corr = 8 * s;
 }
 
 /* Same quantiser, one element per thread: the 16 lanes of a half-warp hold one block. Every

@@ -6,7 +6,7 @@
  * k_quant_act_int8, k_gemv_q4b_dp4a_grp x2, k_moe_gelu_split_batch, k_moe_combine_ord and the
  * recombine norms. CF = src/backends/cuda/cuda_forward.cu of nihilistau/kairos-engine.
  *
- * One CTA per SM, launched cooperatively so all CTAs are co-resident. Each CTA has 16 consumer
+ * One CTA per SM, launched cooperatively so all CTAs are co-resident. Each CTA has 15 consumer
  * warps and one producer warp.
  *
  *   Weights: every CTA owns a fixed slice of each phase's rows. The producer warp streams that
@@ -18,7 +18,7 @@
  *
  *   Activations between CTAs (logits, shared-expert hidden, expert hidden, outputs) travel as
  *   8-byte {value, epoch} words that readers poll: data and flag arrive together, so there is no
- *   separate grid barrier. The residual x lives in every CTA's shared memory across layers.
+ *   separate grid barrier. The residual x lives in registers of every CTA across layers.
  *
  * Per layer:
  *   A (local)  sum x^2 -> ffn_norm / pre_ffw2 / router-prep vectors, int8-quantised in smem
@@ -34,26 +34,29 @@
  * dots per 16, fp32 scale/accumulate in the order of k_gemv_q4b_dp4a_v2: chunk c in lane c%32,
  * then the shuffle tree). Every wait is bounded; a wait that runs out records an error word,
  * after which all waits fall through and the kernel runs to its end.
+ *
+ * The per-layer loop body is executed once per layer by every warp, so its SIZE matters as much
+ * as its instruction count (it streams through the instruction cache): large helpers are kept
+ * out of line and index arithmetic avoids integer division.
  */
 #include "common.cuh"
 #include "decode.cuh"
 
 #ifdef SP_DECODE_STAMPS
-__device__ long long g_sp_stamps[64 * 8];
-#define STAMP(li, k) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (li) < 64) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_sp_stamps[(li) * 8 + (k)] = t_; } } while (0)
-extern "C" int sp_debug_read_stamps(long long *out) { return (int)cudaMemcpyFromSymbol(out, g_sp_stamps, sizeof(long long) * 64 * 8); }
+__device__ long long g_sp_stamps[4 * 64 * 16];
+#define STAMP(li, k) do { if (blockIdx.x % 49 == 0 && threadIdx.x == 0 && (li) < 64) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_sp_stamps[((blockIdx.x / 49) * 64 + (li)) * 16 + (k)] = t_; } } while (0)
+extern "C" int sp_debug_read_stamps(long long *out) { return (int)cudaMemcpyFromSymbol(out, g_sp_stamps, sizeof(long long) * 4 * 64 * 16); }
 #else
 #define STAMP(li, k) do { } while (0)
 #endif
 
 namespace {
 
-constexpr int kCons = 512;                 /* consumer threads */
-constexpr int kCW = kCons / 32;            /* consumer warps */
-constexpr int kThreads = kCons + 32;       /* + one producer warp */
+constexpr int kCW = 15;                    /* consumer warps */
+constexpr int kCons = kCW * 32;            /* consumer threads */
+constexpr int kThreads = kCons + 32;       /* + one producer warp = 16 warps: 4 per scheduler, 128 registers each */
 constexpr int kSlot = 16384;               /* ring slot bytes */
 constexpr int kMaxSlots = 12;
-constexpr int KE = 8;                      /* E <= 4096: at most 8 elements per consumer thread */
 constexpr unsigned kSpinLimit = 1u << 22;  /* polls before a wait gives up (order of a second) */
 
 /* ---------------------------------------------------------------- PTX helpers */
@@ -107,7 +110,7 @@ struct Act {                      /* one quantised activation vector in shared m
 
 struct Smem {
     Ctl *ctl;
-    float *x, *va, *vb;           /* [E] residual, two work vectors */
+    float *va, *vb;               /* [E] two work vectors */
     signed char *q_nx, *q_in, *q_hd, *q_h;
     float *s_nx, *s_in, *s_hd, *s_h;
     int *c_nx, *c_in, *c_hd, *c_h;
@@ -120,37 +123,35 @@ struct Smem {
 
 __host__ __device__ inline size_t al16(size_t v) { return (v + 15) & ~(size_t)15; }
 
-/* one layout function for the device carve and the host size query */
-template <class F>
-__host__ __device__ inline size_t smem_layout(const SpDims &d, int rows_f_max, F place) {
-    size_t o = 0;
-    auto take = [&](int id, size_t bytes) { place(id, o); o = al16(o + bytes); };
-    take(0, sizeof(Ctl));
-    take(1, 4 * (size_t)d.E); take(2, 4 * (size_t)d.E); take(3, 4 * (size_t)d.E);
-    take(4, d.E); take(5, d.E); take(6, d.FFS); take(7, (size_t)d.NU * d.FFE);
-    take(8, 4 * (size_t)(d.E / 16)); take(9, 4 * (size_t)(d.E / 16)); take(10, 4 * (size_t)(d.FFS / 16)); take(11, 4 * (size_t)d.NU * (d.FFE / 16));
-    take(12, 4 * (size_t)(d.E / 16)); take(13, 4 * (size_t)(d.E / 16)); take(14, 4 * (size_t)(d.FFS / 16)); take(15, 4 * (size_t)d.NU * (d.FFE / 16));
-    take(16, 8 * 256); take(17, 8 * (size_t)d.NE);
-    take(18, 4 * (size_t)d.NE); take(19, 4 * (size_t)d.NE); take(20, 4 * (size_t)d.NE);
-    take(21, 4 * (size_t)d.NU * rows_f_max);
-    o = (o + 127) & ~(size_t)127;
-    place(22, o);                                    /* ring starts here */
-    return o;
+/* one layout for the device carve and the host size query: offsets into dynamic shared memory */
+struct SmemOff { size_t o[23]; size_t ring; };
+__host__ __device__ inline SmemOff smem_layout(const SpDims &d, int rows_f_max) {
+    SmemOff L; size_t o = 0; int id = 0;
+    auto take = [&](size_t bytes) { L.o[id++] = o; o = al16(o + bytes); };
+    take(sizeof(Ctl));
+    take(4 * (size_t)d.E); take(4 * (size_t)d.E);
+    take(d.E); take(d.E); take(d.FFS); take((size_t)d.NU * d.FFE);
+    take(4 * (size_t)(d.E / 16)); take(4 * (size_t)(d.E / 16)); take(4 * (size_t)(d.FFS / 16)); take(4 * (size_t)d.NU * (d.FFE / 16));
+    take(4 * (size_t)(d.E / 16)); take(4 * (size_t)(d.E / 16)); take(4 * (size_t)(d.FFS / 16)); take(4 * (size_t)d.NU * (d.FFE / 16));
+    take(8 * 256); take(8 * (size_t)d.NE);
+    take(4 * (size_t)d.NE); take(4 * (size_t)d.NE); take(4 * (size_t)d.NE);
+    take(4 * (size_t)d.NU * rows_f_max);
+    L.ring = (o + 127) & ~(size_t)127;
+    return L;
 }
-
 __device__ Smem carve(unsigned char *base, const SpDims &d, int rows_f_max) {
-    Smem s;
-    unsigned char *ptr[23];
-    smem_layout(d, rows_f_max, [&](int id, size_t off) { ptr[id] = base + off; });
-    s.ctl = (Ctl *)ptr[0];
-    s.x = (float *)ptr[1]; s.va = (float *)ptr[2]; s.vb = (float *)ptr[3];
-    s.q_nx = (signed char *)ptr[4]; s.q_in = (signed char *)ptr[5]; s.q_hd = (signed char *)ptr[6]; s.q_h = (signed char *)ptr[7];
-    s.s_nx = (float *)ptr[8]; s.s_in = (float *)ptr[9]; s.s_hd = (float *)ptr[10]; s.s_h = (float *)ptr[11];
-    s.c_nx = (int *)ptr[12]; s.c_in = (int *)ptr[13]; s.c_hd = (int *)ptr[14]; s.c_h = (int *)ptr[15];
-    s.red = (double *)ptr[16]; s.ex = (double *)ptr[17];
-    s.p = (float *)ptr[18]; s.lg = (float *)ptr[19]; s.dsc = (float *)ptr[20];
-    s.out = (float *)ptr[21];
-    s.ring = ptr[22];
+    const SmemOff L = smem_layout(d, rows_f_max);
+    Smem s; int id = 0;
+    auto nx = [&]() { return base + L.o[id++]; };
+    s.ctl = (Ctl *)nx();
+    s.va = (float *)nx(); s.vb = (float *)nx();
+    s.q_nx = (signed char *)nx(); s.q_in = (signed char *)nx(); s.q_hd = (signed char *)nx(); s.q_h = (signed char *)nx();
+    s.s_nx = (float *)nx(); s.s_in = (float *)nx(); s.s_hd = (float *)nx(); s.s_h = (float *)nx();
+    s.c_nx = (int *)nx(); s.c_in = (int *)nx(); s.c_hd = (int *)nx(); s.c_h = (int *)nx();
+    s.red = (double *)nx(); s.ex = (double *)nx();
+    s.p = (float *)nx(); s.lg = (float *)nx(); s.dsc = (float *)nx();
+    s.out = (float *)nx();
+    s.ring = base + L.ring;
     return s;
 }
 
@@ -185,32 +186,43 @@ __device__ Geo make_geo(const SpDims &d, int b, int G) {
     return g;
 }
 
-/* chunk walkers: the producer and every consumer warp step through the same sequence */
-struct PairWalk {                 /* items [pos, end()) never cross a multiple of `period` */
-    int pos, last, period, per, cid;
-    __device__ PairWalk(int p0, int n, int period_, int per_, int cid_) : pos(p0), last(p0 + n), period(period_), per(per_), cid(cid_) {}
-    __device__ bool valid() const { return pos < last; }
-    __device__ int end() const { int e = pos + per; const int eb = (pos / period + 1) * period; e = e < eb ? e : eb; return e < last ? e : last; }
-    __device__ void next() { pos = end(); cid++; }
+/* position in the ring: slot index and the parity of its current use */
+struct Ring {
+    int slot, ns; unsigned par; bool wrapped;
+    __device__ void adv() { if (++slot == ns) { slot = 0; par ^= 1u; wrapped = true; } }
 };
-struct FWalk {                    /* units u = slot*nj + jj; a chunk = XF experts x all rows, or 1 expert x RF rows */
-    int u, last, nj, RF, XF, NU, cid;
-    __device__ FWalk(const Geo &g, int NU_, int cid_) : u(0), last(NU_ * g.nj), nj(g.nj), RF(g.RF), XF(g.XF), NU(NU_), cid(cid_) {}
-    __device__ bool valid() const { return u < last; }
-    __device__ int end() const {
-        const int s = u / nj;
-        if (RF == nj) { int xs = NU - s; xs = xs < XF ? xs : XF; return (s + xs) * nj; }
-        const int jr = u - s * nj; int rf = nj - jr; rf = rf < RF ? rf : RF; return u + rf;
+/* chunk walkers: the producer and every consumer warp step through the same sequence.
+ * Items [pos, end()) are one chunk: at most `per` items and never across a multiple of `period`. */
+struct SegWalk {
+    int pos, last, per, period, bnd, seg; Ring r;
+    __device__ SegWalk(int p0, int n, int period_, int per_, Ring r_) : pos(p0), last(p0 + n), per(per_), period(period_), r(r_) {
+        if (period_ >= (1 << 30)) { seg = 0; bnd = 0x7fffffff; }
+        else { seg = p0 / period_; bnd = (seg + 1) * period_; }
     }
-    __device__ void next() { u = end(); cid++; }
+    __device__ bool valid() const { return pos < last; }
+    __device__ int end() const { int e = pos + per; e = e < bnd ? e : bnd; return e < last ? e : last; }
+    __device__ int seg_off() const { return pos - (bnd - period); }           /* pos - seg*period */
+    __device__ void next() { pos = end(); if (pos == bnd) { seg++; bnd += period; } r.adv(); }
+};
+/* routed down rows: a chunk = xs experts x all nj rows (when they fit), or 1 expert x rf rows */
+struct FWalk {
+    int s, jr, nj, RF, XF, NU; Ring r;
+    __device__ FWalk(const Geo &g, int NU_, Ring r_) : s(0), jr(0), nj(g.nj), RF(g.RF), XF(g.XF), NU(NU_), r(r_) {}
+    __device__ bool whole() const { return RF == nj; }
+    __device__ bool valid() const { return s < NU && nj > 0; }
+    __device__ int xs() const { if (!whole()) return 1; const int m = NU - s; return m < XF ? m : XF; }
+    __device__ int rf() const { if (whole()) return nj; const int m = nj - jr; return m < RF ? m : RF; }
+    __device__ bool holds(int slot, int jj) const { return whole() ? (slot < s + xs()) : (slot < s || (slot == s && jj < jr + rf())); }
+    __device__ void next() { if (whole()) s += xs(); else { jr += rf(); if (jr >= nj) { jr = 0; s++; } } r.adv(); }
 };
 
 /* ---------------------------------------------------------------- bounded waits */
-__device__ __forceinline__ bool wait_bar(uint64_t *bar, unsigned parity, Ctl *ctl, int *status) {
+__device__ __noinline__ bool wait_bar(uint64_t *bar, unsigned parity, Ctl *ctl, int *status, unsigned backoff_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*(volatile int *)&ctl->abort) return false;
     for (unsigned spins = 0; spins < kSpinLimit; spins++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
         if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) return false;
     }
     *(volatile int *)&ctl->abort = 1;
@@ -218,7 +230,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, unsigned parity, Ctl *ct
     return false;
 }
 /* {value, epoch} word another CTA publishes; polls until the epoch matches */
-__device__ __forceinline__ float ll_read(const unsigned long long *p, unsigned epoch, Ctl *ctl, int *status) {
+__device__ __noinline__ float ll_read(const unsigned long long *p, unsigned epoch, Ctl *ctl, int *status) {
     for (unsigned spins = 0; spins < kSpinLimit; spins++) {
         const unsigned long long v = ld_relaxed_u64(p);
         if ((unsigned)(v >> 32) == epoch) return __uint_as_float((unsigned)v);
@@ -233,159 +245,227 @@ __device__ __forceinline__ void ll_write(unsigned long long *p, float v, unsigne
 }
 
 /* ---------------------------------------------------------------- consumer-side math */
-/* sum of squares in the reference's order (k_rmsnorm, CF:503-511): 256 strided double
- * partials, then sh[t] += sh[t+o] for o = 128 .. 1. All consumer threads must call. */
-__device__ double block_sumsq(const float *v, int n, double *sh) {
-    const int t = threadIdx.x;
-    if (t < 256) { double s = 0.0; for (int i = t; i < n; i += 256) { const double a = v[i]; s += a * a; } sh[t] = s; }
+/* Sum over the consumer threads in double, fixed order: shuffle tree inside each warp, then the
+ * warp totals in warp order. (k_rmsnorm, CF:503-511, sums 256 strided partials with a halving
+ * tree; both are double sums of the same squares, rounded to float right after, so the float
+ * result is the same unless the two double sums straddle a float rounding boundary.)
+ * `sh` has room for the warp totals and is not reused before the next consumer barrier. */
+__device__ __forceinline__ double block_sum(double v, double *sh) {
+    v = warp_sum_f64(v);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
     cons_sync();
-    if (t < 128) sh[t] += sh[t + 128];
-    cons_sync();
-    if (t < 64) sh[t] += sh[t + 64];
-    cons_sync();
-    if (t < 32) {
-        double a = sh[t] + sh[t + 32];
+    double r = 0.0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_down_sync(0xffffffffu, a, o);
-        if (t == 0) sh[0] = a;
-    }
-    cons_sync();
-    const double r = sh[0];
-    cons_sync();
+    for (int w = 0; w < kCW; w++) r += sh[w];
     return r;
 }
-__device__ __forceinline__ float rms_scale_from(double ss, int n, float eps) {
+__device__ __noinline__ float rms_scale_from(double ss, int n, float eps) {
     const float ms = (float)(ss / (double)n);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
 }
-__device__ __forceinline__ float warp_tree(float v) {      /* CF:1711: lane 0 holds the row sum */
+__device__ __noinline__ float gelu_mul_ni(float g, float u) { return gelu_mul(g, u); }
+/* one 32-weight chunk of a Q4B row against the activation: wbsc * (a0*sx0 + a1*sx1), contracted
+ * as the reference's kernel is (moe_cpu_expert.h:14-18) */
+__device__ __forceinline__ float chunk_term(const int4 &w, unsigned short sc, const int4 &qa, const int4 &qb,
+                                            const int2 &corr, const float2 &sx, float facc) {
+    int a0, a1;
+    q4b_chunk_dot(w, qa, qb, corr.x, corr.y, a0, a1);
+    return __fmaf_rn(h2f(sc), __fmaf_rn((float)a0, sx.x, __fmul_rn((float)a1, sx.y)), facc);
+}
+/* R rows (codes and f16 block scales in shared memory), each against its own int8 activation, in
+ * the order of k_gemv_q4b_dp4a_v2 (CF:1697-1711): chunk c accumulates in lane c%32 in increasing
+ * c, then the shuffle tree. The rows are independent, so their loads, integer dots and trees
+ * interleave: that instruction-level parallelism is what hides latency at 4 warps per scheduler. */
+template <int NIT, int R>
+__device__ __forceinline__ void rows_dot(const unsigned char *const (&codes)[R], const unsigned char *const (&scales)[R], const Act (&act)[R],
+                                         int n32, int lane, float (&out)[R]) {
+    float facc[R];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
-    return v;
-}
-/* Q4B row (codes and f16 block scales in shared memory) . int8 activation, in the order of
- * k_gemv_q4b_dp4a_v2 (CF:1697-1711): chunk c accumulates in lane c%32 in increasing c. */
-__device__ __forceinline__ float row_dot(const unsigned char *codes, const unsigned char *scales, int n32, int lane, const Act &a) {
-    float facc = 0.0f;
-    for (int c = lane; c < n32; c += 32) {
-        const int4 w = *reinterpret_cast<const int4 *>(codes + 16 * c);
-        const unsigned short sc = *reinterpret_cast<const unsigned short *>(scales + 2 * c);
-        const int2 corr = *reinterpret_cast<const int2 *>(a.corr + 2 * c);
-        const float2 sx = *reinterpret_cast<const float2 *>(a.sx + 2 * c);
-        int a0, a1;
-        q4b_chunk_dot(w, a.q[2 * c], a.q[2 * c + 1], corr.x, corr.y, a0, a1);
-        const float t = __fmaf_rn((float)a0, sx.x, __fmul_rn((float)a1, sx.y));
-        facc = __fmaf_rn(h2f(sc), t, facc);
+    for (int r = 0; r < R; r++) facc[r] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int c = lane + 32 * i;
+        if (c < n32) {
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int4 w = *reinterpret_cast<const int4 *>(codes[r] + 16 * c);
+                const unsigned short sc = *reinterpret_cast<const unsigned short *>(scales[r] + 2 * c);
+                facc[r] = chunk_term(w, sc, act[r].q[2 * c], act[r].q[2 * c + 1], *reinterpret_cast<const int2 *>(act[r].corr + 2 * c),
+                                     *reinterpret_cast<const float2 *>(act[r].sx + 2 * c), facc[r]);
+            }
+        }
     }
-    return warp_tree(facc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < R; r++) facc[r] += __shfl_down_sync(0xffffffffu, facc[r], o);
+#pragma unroll
+    for (int r = 0; r < R; r++) out[r] = facc[r];
 }
-/* gate and up rows against the same activation: the activation block is read once */
-__device__ __forceinline__ float pair_dot_gelu(const unsigned char *gc, const unsigned char *gs, const unsigned char *uc, const unsigned char *us,
-                                               int n32, int lane, const Act &a) {
-    float fg = 0.0f, fu = 0.0f;
-    for (int c = lane; c < n32; c += 32) {
-        const int4 wg = *reinterpret_cast<const int4 *>(gc + 16 * c);
-        const int4 wu = *reinterpret_cast<const int4 *>(uc + 16 * c);
-        const unsigned short sg = *reinterpret_cast<const unsigned short *>(gs + 2 * c);
-        const unsigned short su = *reinterpret_cast<const unsigned short *>(us + 2 * c);
-        const int2 corr = *reinterpret_cast<const int2 *>(a.corr + 2 * c);
-        const float2 sx = *reinterpret_cast<const float2 *>(a.sx + 2 * c);
-        const int4 qa = a.q[2 * c], qb = a.q[2 * c + 1];
-        int a0, a1;
-        q4b_chunk_dot(wg, qa, qb, corr.x, corr.y, a0, a1);
-        fg = __fmaf_rn(h2f(sg), __fmaf_rn((float)a0, sx.x, __fmul_rn((float)a1, sx.y)), fg);
-        q4b_chunk_dot(wu, qa, qb, corr.x, corr.y, a0, a1);
-        fu = __fmaf_rn(h2f(su), __fmaf_rn((float)a0, sx.x, __fmul_rn((float)a1, sx.y)), fu);
+/* two gate/up row pairs against ONE activation (read once per chunk); out = gelu(gate) * up.
+ * Out of line: it has two callers (shared expert, routed experts). */
+struct PairPtrs { const unsigned char *gc, *gs, *uc, *us; };
+template <int NIT>
+__device__ __noinline__ float2 pairs2_gelu(PairPtrs p0, PairPtrs p1, const int4 *aq, const float *asx, const int *acorr, int n32, int lane) {
+    float fg0 = 0.0f, fu0 = 0.0f, fg1 = 0.0f, fu1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NIT; i++) {
+        const int c = lane + 32 * i;
+        if (c < n32) {
+            const int2 corr = *reinterpret_cast<const int2 *>(acorr + 2 * c);
+            const float2 sx = *reinterpret_cast<const float2 *>(asx + 2 * c);
+            const int4 qa = aq[2 * c], qb = aq[2 * c + 1];
+            fg0 = chunk_term(*reinterpret_cast<const int4 *>(p0.gc + 16 * c), *reinterpret_cast<const unsigned short *>(p0.gs + 2 * c), qa, qb, corr, sx, fg0);
+            fu0 = chunk_term(*reinterpret_cast<const int4 *>(p0.uc + 16 * c), *reinterpret_cast<const unsigned short *>(p0.us + 2 * c), qa, qb, corr, sx, fu0);
+            fg1 = chunk_term(*reinterpret_cast<const int4 *>(p1.gc + 16 * c), *reinterpret_cast<const unsigned short *>(p1.gs + 2 * c), qa, qb, corr, sx, fg1);
+            fu1 = chunk_term(*reinterpret_cast<const int4 *>(p1.uc + 16 * c), *reinterpret_cast<const unsigned short *>(p1.us + 2 * c), qa, qb, corr, sx, fu1);
+        }
     }
-    const float g = warp_tree(fg), u = warp_tree(fu);
-    return gelu_mul(g, u);                                   /* meaningful in lane 0 */
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        fg0 += __shfl_down_sync(0xffffffffu, fg0, o); fu0 += __shfl_down_sync(0xffffffffu, fu0, o);
+        fg1 += __shfl_down_sync(0xffffffffu, fg1, o); fu1 += __shfl_down_sync(0xffffffffu, fu1, o);
+    }
+    return make_float2(gelu_mul_ni(fg0, fu0), gelu_mul_ni(fg1, fu1));      /* meaningful in lane 0 */
 }
+
 /* router row in fp32, fixed order: lane l takes the float4 groups q = l, l+32, ... with
  * acc = fma(w, x, acc) over the four elements in order, then the shuffle tree. */
 __device__ __forceinline__ float router_row(const float *wrow, const float *rin, int E, int lane) {
     float acc = 0.0f;
+#pragma unroll 1
     for (int q = lane; q < (E >> 2); q += 32) {
         const float4 w = *reinterpret_cast<const float4 *>(wrow + 4 * q);
         const float4 xv = *reinterpret_cast<const float4 *>(rin + 4 * q);
         acc = __fmaf_rn(w.x, xv.x, acc); acc = __fmaf_rn(w.y, xv.y, acc);
         acc = __fmaf_rn(w.z, xv.z, acc); acc = __fmaf_rn(w.w, xv.w, acc);
     }
-    return warp_tree(acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    return acc;
 }
-/* quantise a vector (read through `get`) into de-interleaved int8 blocks in shared memory */
-template <class F>
-__device__ __forceinline__ void quant_vec(int n, signed char *q, float *sx, int *corr, F get) {
-    for (int base = 0; base < n; base += kCons) {
-        const int i = base + (int)threadIdx.x;
-        const bool valid = i < n;
-        const float v = valid ? get(i) : 0.0f;
-        const int b = i >> 4;
-        quant_elem16(v, valid, q + 16 * b, sx + b, corr + b);
+/* poll 16 consecutive {value, epoch} words (all loads in flight together, repeated until every tag
+ * matches) and quantise them as one block. Out of line: it is big and has two callers. */
+__device__ __noinline__ void ll_quant16(const unsigned long long *p, unsigned epoch, int4 *dst, float *sx, int *corr, Ctl *ctl, int *status) {
+    float v[16];
+    for (unsigned spins = 0; spins < kSpinLimit; spins++) {
+        unsigned long long w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) w[i] = ld_relaxed_u64(p + i);
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < 16; i++) { ok = ok && ((unsigned)(w[i] >> 32) == epoch); v[i] = __uint_as_float((unsigned)w[i]); }
+        if (ok) break;
+        if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) break;
+        if (spins == kSpinLimit - 1) { *(volatile int *)&ctl->abort = 1; atomicExch(status, SP_KERR_BARRIER_TIMEOUT); }
     }
+    quant_block16_store(v, dst, sx, corr);
+}
+/* quantise one 16-block held in shared memory as floats */
+__device__ __noinline__ void quant_smem_block(const float *src, int b, signed char *q, float *sx, int *corr) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float4 f = reinterpret_cast<const float4 *>(src + 16 * b)[i]; v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w; }
+    quant_block16_store(v, reinterpret_cast<int4 *>(q) + b, sx + b, corr + b);
 }
 
-/* moe_topk_host (CF:6220-6240) on the device, run redundantly by every CTA. s.lg holds the
- * logits, s.dsc the per-expert down scales. */
-__device__ void topk_block(const SpDims &d, Smem &s, int *status) {
-    const int NE = d.NE, NU = d.NU, t = threadIdx.x;
+/* moe_topk_host (CF:6220-6240) on the device, run redundantly by every CTA, by the first `tw`
+ * consumer warps (they synchronise on their own named barrier so the other warps can quantise
+ * the shared-expert activation meanwhile). Polls the logits itself; s.dsc holds the per-expert
+ * down scales. */
+__device__ __noinline__ void topk_warps(const SpDecodeArgs &a, const SpDims &d, Smem &s, unsigned epoch, int tw) {
+    const int NE = d.NE, NU = d.NU, t = threadIdx.x, T = 32 * tw;
     Ctl *ctl = s.ctl;
-    float *wmaxf = reinterpret_cast<float *>(s.red);
+    auto tsync = [&]() { asm volatile("bar.sync 2, %0;" ::"r"(T) : "memory"); };
+    float *wmaxf = reinterpret_cast<float *>(s.red + 64);
+    double *wsum = s.red + 96;
     float mx = -INFINITY; int bad = 0;
-    for (int i = t; i < NE; i += kCons) { const float l = s.lg[i]; if (l != l) bad = 1; mx = fmaxf(mx, l); }
+#pragma unroll 1
+    for (int i = t; i < NE; i += T) { const float l = ll_read(a.x_logits + i, epoch, ctl, a.status); s.lg[i] = l; if (l != l) bad = 1; mx = fmaxf(mx, l); }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) { mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o)); bad |= __shfl_xor_sync(0xffffffffu, bad, o); }
     if ((t & 31) == 0) wmaxf[t >> 5] = mx;
-    if (bad && (t & 31) == 0) atomicExch(status, SP_KERR_NAN_ROUTER);
-    cons_sync();
+    if (bad && (t & 31) == 0) atomicExch(a.status, SP_KERR_NAN_ROUTER);
+    if (t < SP_MAX_NU) { ctl->sel_desc[t] = t < NE ? t : 0; ctl->p_desc[t] = 0.0f; }
+    tsync();
     mx = wmaxf[0];
-#pragma unroll
-    for (int w = 1; w < kCW; w++) mx = fmaxf(mx, wmaxf[w]);
-    cons_sync();
+    for (int w = 1; w < tw; w++) mx = fmaxf(mx, wmaxf[w]);
     /* exp in double, summed in double in a fixed order (strided partials, shuffle tree, warps in order) */
     double part = 0.0;
-    for (int i = t; i < NE; i += kCons) { const double e = exp((double)s.lg[i] - (double)mx); s.ex[i] = e; part += e; }
+#pragma unroll 1
+    for (int i = t; i < NE; i += T) { const double e = exp((double)s.lg[i] - (double)mx); s.ex[i] = e; part += e; }
     part = warp_sum_f64(part);
-    if ((t & 31) == 0) s.red[t >> 5] = part;
-    cons_sync();
+    if ((t & 31) == 0) wsum[t >> 5] = part;
+    tsync();
     double sum = 0.0;
-#pragma unroll
-    for (int w = 0; w < kCW; w++) sum += s.red[w];
-    for (int i = t; i < NE; i += kCons) s.p[i] = (float)(s.ex[i] / sum);
-    if (t < SP_MAX_NU) { ctl->sel_desc[t] = t < NE ? t : 0; ctl->p_desc[t] = 0.0f; }
-    cons_sync();
+    for (int w = 0; w < tw; w++) sum += wsum[w];
+#pragma unroll 1
+    for (int i = t; i < NE; i += T) s.p[i] = (float)(s.ex[i] / sum);
+    tsync();
     /* insertion with strict > == rank by (p desc, id asc) */
-    for (int i = t; i < NE; i += kCons) {
+#pragma unroll 1
+    for (int i = t; i < NE; i += T) {
         const float pi = s.p[i]; int r = 0;
-        for (int j = 0; j < NE; j++) { const float pj = s.p[j]; r += (pj > pi) || (pj == pi && j < i); }
+#pragma unroll 1
+        for (int j4 = 0; j4 + 3 < NE; j4 += 4) {
+            const float4 pj = *reinterpret_cast<const float4 *>(s.p + j4);
+            r += (pj.x > pi) || (pj.x == pi && j4 < i);
+            r += (pj.y > pi) || (pj.y == pi && j4 + 1 < i);
+            r += (pj.z > pi) || (pj.z == pi && j4 + 2 < i);
+            r += (pj.w > pi) || (pj.w == pi && j4 + 3 < i);
+        }
+        for (int j = NE & ~3; j < NE; j++) { const float pj = s.p[j]; r += (pj > pi) || (pj == pi && j < i); }
         if (r < NU && pi == pi) { ctl->sel_desc[r] = i; ctl->p_desc[r] = pi; }
     }
-    cons_sync();
-    float wnorm = 0.0f;
-    if (t < NU) {
-        float wsum = 0.0f;
-        for (int k = 0; k < NU; k++) wsum = __fadd_rn(wsum, ctl->p_desc[k]);
-        if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
-        const int e = ctl->sel_desc[t];
-        wnorm = __fdiv_rn(ctl->p_desc[t], wsum);
-        int slot = 0;
-        for (int j = 0; j < NU; j++) slot += (ctl->sel_desc[j] < e);
-        ctl->sel_asc[slot] = e;
-        ctl->cw[slot] = __fmul_rn(wnorm, s.dsc[e]);        /* w * dexps_scale[e], CF:8709 */
+    tsync();
+    if (t < 32) {                                          /* NU <= 8 lanes of warp 0 */
+        float wnorm = 0.0f; int e = 0, slot = 0;
+        if (t < NU) {
+            float ws = 0.0f;
+            for (int k = 0; k < NU; k++) ws = __fadd_rn(ws, ctl->p_desc[k]);
+            if (ws < 6.103515625e-5f) ws = 6.103515625e-5f;
+            e = ctl->sel_desc[t];
+            wnorm = __fdiv_rn(ctl->p_desc[t], ws);
+            for (int j = 0; j < NU; j++) slot += (ctl->sel_desc[j] < e);
+        }
+        __syncwarp();
+        if (t < NU) {
+            ctl->sel_asc[slot] = e;
+            ctl->cw[slot] = __fmul_rn(wnorm, s.dsc[e]);    /* w * dexps_scale[e], CF:8709 */
+            ctl->p_desc[t] = wnorm;                        /* renormalised, descending order */
+        }
+        __syncwarp();
+        if (t == 0) mbar_arrive(&ctl->sel_ready);          /* the producer may now fetch the routed rows */
     }
-    cons_sync();
-    if (t < NU) ctl->p_desc[t] = wnorm;                    /* renormalised, descending order */
-    cons_sync();
+}
+
+/* layer li of this launch: the arena is one slab per layer, so a layer's pointers are layer 0's
+ * plus a stride; nothing is loaded from memory */
+__device__ __forceinline__ SpLayerDev layer_at(const SpDecodeArgs &a, int li) {
+    const size_t off = (size_t)(a.layer_first + li) * a.layer_stride;
+    SpLayerDev L = a.layer0;
+    auto f = [&](const float *p) { return reinterpret_cast<const float *>(reinterpret_cast<const unsigned char *>(p) + off); };
+    auto u8 = [&](const uint8_t *p) { return p + off; };
+    auto u16 = [&](const uint16_t *p) { return reinterpret_cast<const uint16_t *>(reinterpret_cast<const unsigned char *>(p) + off); };
+    L.router_w = f(L.router_w); L.router_scale = f(L.router_scale);
+    L.router_bias = ((a.bias_mask >> li) & 1ull) ? f(L.router_bias) : nullptr;
+    L.ffn_norm = f(L.ffn_norm); L.post_ffw1 = f(L.post_ffw1); L.pre_ffw2 = f(L.pre_ffw2); L.post_ffw2 = f(L.post_ffw2);
+    L.post_ffw = f(L.post_ffw); L.dexps_scale = f(L.dexps_scale);
+    L.gu_codes = u8(L.gu_codes); L.gu_bs = u16(L.gu_bs); L.dn_codes = u8(L.dn_codes); L.dn_bs = u16(L.dn_bs);
+    L.sg_codes = u8(L.sg_codes); L.sg_bs = u16(L.sg_bs); L.su_codes = u8(L.su_codes); L.su_bs = u16(L.su_bs);
+    L.sd_codes = u8(L.sd_codes); L.sd_bs = u16(L.sd_bs);
+    return L;
 }
 
 /* ---------------------------------------------------------------- the producer warp's lane */
 struct Producer {
-    Ctl *ctl; unsigned char *ring; int ns; int cid; int *status; bool ok;
+    Ctl *ctl; unsigned char *ring; Ring r; int *status; bool ok; int issued;
     __device__ unsigned char *acquire() {
-        const int slot = cid % ns;
-        if (cid >= ns && ok) ok = wait_bar(&ctl->empty[slot], (unsigned)((cid / ns - 1) & 1), ctl, status);
-        return ring + (size_t)slot * kSlot;
+        if (r.wrapped && ok) ok = wait_bar(&ctl->empty[r.slot], r.par ^ 1u, ctl, status, 64);
+        return ring + (size_t)r.slot * kSlot;
     }
-    __device__ uint64_t *bar() { return &ctl->full[cid % ns]; }
+    __device__ uint64_t *bar() { return &ctl->full[r.slot]; }
+    __device__ void done() { r.adv(); issued++; }
     /* nbytes of scale rows starting at `src` (any alignment): the enclosing 16-byte-aligned span */
     __device__ unsigned scale_span(const unsigned char *src, int nbytes, const unsigned char *&asrc) {
         const unsigned delta = (unsigned)((uintptr_t)src & 15);
@@ -404,7 +484,7 @@ struct Producer {
             bulk_g2s(dst + 2 * cb, ags, bgs, bar());
             bulk_g2s(dst + 2 * cb + sr, aus, bus, bar());
         }
-        cid++;
+        done();
     }
     __device__ void rows(const unsigned char *c, const unsigned char *sc, int n, int rb, int sb) {
         unsigned char *dst = acquire();
@@ -415,7 +495,7 @@ struct Producer {
             bulk_g2s(dst, c, cb, bar());
             bulk_g2s(dst + cb, as, bs, bar());
         }
-        cid++;
+        done();
     }
     __device__ void rows2(const unsigned char *c0, const unsigned char *s0, const unsigned char *c1, const unsigned char *s1, int n, int rb, int sb) {
         unsigned char *dst = acquire();
@@ -429,82 +509,81 @@ struct Producer {
             bulk_g2s(dst + blk, c1, cb, bar());
             bulk_g2s(dst + blk + cb, a1, b1, bar());
         }
-        cid++;
+        done();
     }
     __device__ void flat(const void *src, unsigned bytes) {
         unsigned char *dst = acquire();
         if (ok) { mbar_expect_tx(bar(), bytes); bulk_g2s(dst, src, bytes, bar()); }
-        cid++;
+        done();
     }
 };
 
-__device__ void producer_main(const SpDecodeArgs &a, const Geo &g, Smem &s, int ns) {
+__device__ __noinline__ void producer_main(const SpDecodeArgs &a, const Geo &g, Smem &s, int ns) {
     const SpDims &d = a.d;
-    Producer P{s.ctl, s.ring, ns, 0, a.status, true};
+    Producer P{s.ctl, s.ring, Ring{0, ns, 0u, false}, a.status, true, 0};
+    const Ring nil{0, 1, 0u, false};
+#pragma unroll 1
     for (int li = 0; li < a.n_layers; li++) {
-        const SpLayerDev L = a.layers[a.layer_first + li];
+        const SpLayerDev L = layer_at(a, li);
         /* B: router rows, then shared-expert gate/up pairs */
         for (int r = 0; r < g.nr; r++) P.flat(L.router_w + (size_t)(g.r0 + r) * d.E, (unsigned)d.E * 4u);
-        for (PairWalk w(g.p0, g.np, 1 << 30, g.PB, 0); w.valid(); w.next()) {
+        for (SegWalk w(g.p0, g.np, 1 << 30, g.PB, nil); w.valid(); w.next()) {
             const size_t c = (size_t)w.pos; const int n = w.end() - w.pos;
             P.pairs(L.sg_codes + c * g.rbE, (const unsigned char *)L.sg_bs + c * g.sbE,
                     L.su_codes + c * g.rbE, (const unsigned char *)L.su_bs + c * g.sbE, n, g.rbE, g.sbE);
         }
         /* D, routing-independent part: shared-expert down rows */
-        for (PairWalk w(g.j0, g.nj, 1 << 30, g.RS, 0); w.valid(); w.next()) {
+        for (SegWalk w(g.j0, g.nj, 1 << 30, g.RS, nil); w.valid(); w.next()) {
             const size_t j = (size_t)w.pos;
             P.rows(L.sd_codes + j * g.rbS, (const unsigned char *)L.sd_bs + j * g.sbS, w.end() - w.pos, g.rbS, g.sbS);
         }
         /* the selection of this layer */
-        if (P.ok) P.ok = wait_bar(&s.ctl->sel_ready, (unsigned)(li & 1), s.ctl, a.status);
-        int sel[SP_MAX_NU];
-#pragma unroll
-        for (int k = 0; k < SP_MAX_NU; k++) sel[k] = k < d.NU ? *(volatile int *)&s.ctl->sel_asc[k] : 0;
+        if (P.ok) P.ok = wait_bar(&s.ctl->sel_ready, (unsigned)(li & 1), s.ctl, a.status, 32);
         /* D: routed gate|up pairs */
-        for (PairWalk w(g.P0, g.nP, d.FFE, g.PB, 0); w.valid(); w.next()) {
-            const int slot = w.pos / d.FFE, c = w.pos - slot * d.FFE, n = w.end() - w.pos;
-            int e = 0;
-#pragma unroll
-            for (int k = 0; k < SP_MAX_NU; k++) if (k == slot) e = sel[k];
+        for (SegWalk w(g.P0, g.nP, d.FFE, g.PB, nil); w.valid(); w.next()) {
+            const int c = w.seg_off(), n = w.end() - w.pos;
+            const int e = *(volatile int *)&s.ctl->sel_asc[w.seg];
             const size_t grow = (size_t)e * 2 * d.FFE + c, urow = grow + d.FFE;
             P.pairs(L.gu_codes + grow * g.rbE, (const unsigned char *)L.gu_bs + grow * g.sbE,
                     L.gu_codes + urow * g.rbE, (const unsigned char *)L.gu_bs + urow * g.sbE, n, g.rbE, g.sbE);
         }
         /* F: routed down rows */
-        for (FWalk w(g, d.NU, 0); w.valid(); w.next()) {
-            const int slot = w.u / g.nj, jr = w.u - slot * g.nj;
-            int e0 = 0, e1 = 0;
-#pragma unroll
-            for (int k = 0; k < SP_MAX_NU; k++) { if (k == slot) e0 = sel[k]; if (k == slot + 1) e1 = sel[k]; }
-            const size_t row0 = (size_t)e0 * d.E + g.j0 + jr;
-            if (g.RF == g.nj && w.end() - w.u == 2 * g.nj) {
+        for (FWalk w(g, d.NU, nil); w.valid(); w.next()) {
+            const int e0 = *(volatile int *)&s.ctl->sel_asc[w.s];
+            const size_t row0 = (size_t)e0 * d.E + g.j0 + w.jr;
+            if (w.xs() == 2) {
+                const int e1 = *(volatile int *)&s.ctl->sel_asc[w.s + 1];
                 const size_t row1 = (size_t)e1 * d.E + g.j0;
                 P.rows2(L.dn_codes + row0 * g.rbF, (const unsigned char *)L.dn_bs + row0 * g.sbF,
                         L.dn_codes + row1 * g.rbF, (const unsigned char *)L.dn_bs + row1 * g.sbF, g.nj, g.rbF, g.sbF);
             } else {
-                P.rows(L.dn_codes + row0 * g.rbF, (const unsigned char *)L.dn_bs + row0 * g.sbF, w.end() - w.u, g.rbF, g.sbF);
+                P.rows(L.dn_codes + row0 * g.rbF, (const unsigned char *)L.dn_bs + row0 * g.sbF, w.rf(), g.rbF, g.sbF);
             }
         }
     }
-    /* leave only when every copy this lane started has landed (they all have, unless a wait ran out) */
-    const int first = P.cid > ns ? P.cid - ns : 0;
-    for (int c = first; c < P.cid; c++) {
-        uint64_t *bar = &s.ctl->full[c % ns];
-        const unsigned parity = (unsigned)((c / ns) & 1);
-        for (unsigned spins = 0; spins < kSpinLimit; spins++) if (mbar_try_wait(bar, parity)) break;
+    /* leave only when every copy this lane started has landed (they all have, unless a wait ran out):
+     * walk the last ns chunks backwards from the current ring position */
+    Ring q = P.r;
+    const int back = P.issued < ns ? P.issued : ns;
+    for (int i = 0; i < back; i++) {
+        if (q.slot == 0) { q.slot = ns - 1; q.par ^= 1u; } else q.slot--;
+        for (unsigned spins = 0; spins < kSpinLimit; spins++) if (mbar_try_wait(&s.ctl->full[q.slot], q.par)) break;
     }
 }
 
 /* ---------------------------------------------------------------- consumers: ring access */
 struct Consumer {
-    Ctl *ctl; unsigned char *ring; int ns; int *status; int lane;
-    __device__ const unsigned char *wait(int cid) {
-        wait_bar(&ctl->full[cid % ns], (unsigned)((cid / ns) & 1), ctl, status);
-        return ring + (size_t)(cid % ns) * kSlot;
+    Ctl *ctl; unsigned char *ring; int *status; int lane;
+    __device__ const unsigned char *wait(const Ring &r) {
+        wait_bar(&ctl->full[r.slot], r.par, ctl, status, 0);
+        return ring + (size_t)r.slot * kSlot;
     }
-    __device__ void release(int cid) { __syncwarp(); if (lane == 0) mbar_arrive(&ctl->empty[cid % ns]); }
+    __device__ void release(const Ring &r) { __syncwarp(); if (lane == 0) mbar_arrive(&ctl->empty[r.slot]); }
 };
 
+/* KE: elements of an [E] vector each consumer thread owns (E <= KE * 480).
+ * NIT_E / NIT_S / NIT_F: 32-weight chunks per lane for rows of E / FFS / FFE columns. */
+template <int KE, int NIT_E, int NIT_S, int NIT_F>
 __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const SpDims d = a.d;
@@ -530,207 +609,303 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
     }
 
     /* ---------------------------------------------------------------- consumers */
-    Consumer C{ctl, s.ring, ns, a.status, lane};
-    int cid = 0;
-    for (int i = t; i < E; i += kCons) s.x[i] = a.x_in[i];
-    /* norm / scale vectors of the element-wise steps ride in registers: element i = t + 512*k */
-    float wn[KE], wp[KE], rs[KE], w1[KE], w2[KE], w3[KE];
+    Consumer C{ctl, s.ring, a.status, lane};
+    Ring ring{0, ns, 0u, false};                         /* next chunk to consume */
+    const int tw = ((NE + 31) / 32 < 4) ? 4 : (((NE + 31) / 32 > kCW) ? kCW : (NE + 31) / 32);   /* warps that run the top-k */
+    /* the residual and the norm / scale vectors of the element-wise steps ride in registers:
+     * this thread owns elements i = t + 480*k. wn/wp/rs are fetched one layer ahead (in G). */
+    float xr[KE], wn[KE], wp[KE], rs[KE];
     {
-        const SpLayerDev &L0 = a.layers[a.layer_first];
+        const SpLayerDev L0 = layer_at(a, 0);
 #pragma unroll
         for (int k = 0; k < KE; k++) {
             const int i = t + kCons * k;
-            wn[k] = wp[k] = rs[k] = w1[k] = w2[k] = w3[k] = 0.0f;
-            if (i < E) { wn[k] = __ldg(L0.ffn_norm + i); wp[k] = __ldg(L0.pre_ffw2 + i); rs[k] = __ldg(L0.router_scale + i); }
+            xr[k] = wn[k] = wp[k] = rs[k] = 0.0f;
+            if (i < E) { xr[k] = a.x_in[i]; wn[k] = __ldg(L0.ffn_norm + i); wp[k] = __ldg(L0.pre_ffw2 + i); rs[k] = __ldg(L0.router_scale + i); }
         }
     }
-    cons_sync();
 
+#pragma unroll 1
     for (int li = 0; li < a.n_layers; li++) {
-        const SpLayerDev &L = a.layers[a.layer_first + li];
+        const SpLayerDev L = layer_at(a, li);
         const unsigned epoch = a.epoch_base + (unsigned)li + 1u;
         STAMP(li, 0);
         /* ---------------- A: norms of x ---------------- */
         {
-            const float scale = rms_scale_from(block_sumsq(s.x, E, s.red), E, d.eps);
+            float dsc_r[2] = {0.0f, 0.0f};
+            if (t < NE) dsc_r[0] = __ldg(L.dexps_scale + t);
+            if (t + kCons < NE) dsc_r[1] = __ldg(L.dexps_scale + t + kCons);
+            double part = 0.0;
+#pragma unroll
+            for (int k = 0; k < KE; k++) { const double v = xr[k]; part += v * v; }      /* elements past E are 0 */
+            const float scale = rms_scale_from(block_sum(part, s.red), E, d.eps);
+            STAMP(li, 8);
 #pragma unroll
             for (int k = 0; k < KE; k++) {
                 const int i = t + kCons * k;
-                if (kCons * k < E) {                                    /* uniform per CTA: shuffles stay converged */
-                    const bool valid = i < E;
-                    const float xs = valid ? __fmul_rn(s.x[i], scale) : 0.0f;
-                    const int bq = i >> 4;
-                    quant_elem16(valid ? __fmul_rn(xs, wn[k]) : 0.0f, valid, s.q_nx + 16 * bq, s.s_nx + bq, s.c_nx + bq);
-                    quant_elem16(valid ? __fmul_rn(xs, wp[k]) : 0.0f, valid, s.q_in + 16 * bq, s.s_in + bq, s.c_in + bq);
-                    if (valid) s.va[i] = __fmul_rn(__fmul_rn(xs, d.inv_sqrt_e), rs[k]);   /* CF:5952-5953 */
-                }
+                if (i < E) { const float xs = __fmul_rn(xr[k], scale); s.va[i] = __fmul_rn(xs, wn[k]); s.vb[i] = __fmul_rn(xs, wp[k]); }
             }
-            for (int i = t; i < NE; i += kCons) s.dsc[i] = __ldg(L.dexps_scale + i);
             cons_sync();
+            const int nb = E >> 4;
+#pragma unroll 1
+            for (int bq = t; bq < 2 * nb; bq += kCons) {
+                const bool first = bq < nb;
+                quant_smem_block(first ? s.va : s.vb, first ? bq : bq - nb, first ? s.q_nx : s.q_in, first ? s.s_nx : s.s_in, first ? s.c_nx : s.c_in);
+            }
+            cons_sync();
+#pragma unroll
+            for (int k = 0; k < KE; k++) {
+                const int i = t + kCons * k;
+                if (i < E) s.va[i] = __fmul_rn(__fmul_rn(__fmul_rn(xr[k], scale), d.inv_sqrt_e), rs[k]);   /* CF:5952-5953 */
+            }
+            if (t < NE) s.dsc[t] = dsc_r[0];
+            if (t + kCons < NE) s.dsc[t + kCons] = dsc_r[1];
+            for (int i = t + 2 * kCons; i < NE; i += kCons) s.dsc[i] = __ldg(L.dexps_scale + i);
+            cons_sync();
+            STAMP(li, 9);
         }
         STAMP(li, 1);
         /* ---------------- B: router rows + shared gate/up pairs ---------------- */
         {
             const int n32 = E >> 5;
-            const Act act{reinterpret_cast<const int4 *>(s.q_nx), s.s_nx, s.c_nx};
-            for (int r = 0; r < g.nr; r++) {                            /* one slot per router row */
-                if (warp == (r % kCW)) {
-                    const float *wrow = reinterpret_cast<const float *>(C.wait(cid + r));
+#pragma unroll 1
+            for (int r = 0; r < g.nr; r++) {                            /* one slot per router row; warps take turns */
+                if (warp == kCW - 1 - (r % kCW)) {
+                    const float *wrow = reinterpret_cast<const float *>(C.wait(ring));
                     float l = router_row(wrow, s.va, E, lane);
                     if (lane == 0) { if (L.router_bias) l = __fadd_rn(l, __ldg(L.router_bias + g.r0 + r)); ll_write(a.x_logits + g.r0 + r, l, epoch); }
                 }
-                C.release(cid + r);
+                C.release(ring);
+                ring.adv();
             }
-            cid += g.nr;
-            PairWalk w(g.p0, g.np, 1 << 30, g.PB, cid);
-            for (int p = g.p0 + ((warp + kCW - (g.nr % kCW)) % kCW); p < g.p0 + g.np; p += kCW) {
-                while (p >= w.end()) { C.release(w.cid); w.next(); }
-                const unsigned char *base = C.wait(w.cid);
-                const int n = w.end() - w.pos, idx = p - w.pos;
-                const size_t c0 = (size_t)w.pos;
-                const unsigned cb = (unsigned)(n * g.rbE), sr = (unsigned)sr_bytes(n, g.sbE);
-                const unsigned dg = (unsigned)((uintptr_t)((const unsigned char *)L.sg_bs + c0 * g.sbE) & 15);
-                const unsigned du = (unsigned)((uintptr_t)((const unsigned char *)L.su_bs + c0 * g.sbE) & 15);
-                const float h = pair_dot_gelu(base + (size_t)idx * g.rbE, base + 2 * cb + dg + (size_t)idx * g.sbE,
-                                              base + cb + (size_t)idx * g.rbE, base + 2 * cb + sr + du + (size_t)idx * g.sbE, n32, lane, act);
-                if (lane == 0) ll_write(a.x_hd + p, h, epoch);
+            SegWalk w(g.p0, g.np, 1 << 30, g.PB, ring);
+            const int pend = g.p0 + g.np;
+#pragma unroll 1
+            for (int q0 = g.p0 + warp * 2; q0 < pend; q0 += kCW * 2) {
+                PairPtrs pp[2];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int p = (q0 + r < pend) ? q0 + r : q0;
+                    while (p >= w.end()) { C.release(w.r); w.next(); }
+                    const unsigned char *base = C.wait(w.r);
+                    const int n = w.end() - w.pos, idx = p - w.pos;
+                    const size_t c0 = (size_t)w.pos;
+                    const unsigned cb = (unsigned)(n * g.rbE), sr = (unsigned)sr_bytes(n, g.sbE);
+                    const unsigned dg = (unsigned)((uintptr_t)((const unsigned char *)L.sg_bs + c0 * g.sbE) & 15);
+                    const unsigned du = (unsigned)((uintptr_t)((const unsigned char *)L.su_bs + c0 * g.sbE) & 15);
+                    pp[r] = PairPtrs{base + (size_t)idx * g.rbE, base + 2 * cb + dg + (size_t)idx * g.sbE,
+                                     base + cb + (size_t)idx * g.rbE, base + 2 * cb + sr + du + (size_t)idx * g.sbE};
+                }
+                const float2 h = pairs2_gelu<NIT_E>(pp[0], pp[1], reinterpret_cast<const int4 *>(s.q_nx), s.s_nx, s.c_nx, n32, lane);
+                if (lane == 0) { ll_write(a.x_hd + q0, h.x, epoch); if (q0 + 1 < pend) ll_write(a.x_hd + q0 + 1, h.y, epoch); }
             }
-            while (w.valid()) { C.release(w.cid); w.next(); }
-            cid = w.cid;
+            while (w.valid()) { C.release(w.r); w.next(); }
+            ring = w.r;
         }
         STAMP(li, 2);
-        /* ---------------- C: top-k, quantise hd ---------------- */
-        for (int i = t; i < NE; i += kCons) s.lg[i] = ll_read(a.x_logits + i, epoch, ctl, a.status);
+        /* ---------------- C: top-k on the first warps, hd quantisation on the others ---------------- */
+        if (warp < tw) topk_warps(a, d, s, epoch, tw);
+        {
+            const int t0 = (tw < kCW) ? 32 * tw : 0, nt = kCons - t0;
+            if (t >= t0)
+#pragma unroll 1
+                for (int bq = t - t0; bq < (FFS >> 4); bq += nt)
+                    ll_quant16(a.x_hd + 16 * bq, epoch, reinterpret_cast<int4 *>(s.q_hd) + bq, s.s_hd + bq, s.c_hd + bq, ctl, a.status);
+        }
         cons_sync();
-        STAMP(li, 3);
-        topk_block(d, s, a.status);
-        if (t == 0) mbar_arrive(&ctl->sel_ready);                       /* the producer may now fetch the routed rows */
+        STAMP(li, 10);
         if (b == 0 && t < NU) {
             if (a.sel_out) a.sel_out[(size_t)li * NU + t] = ctl->sel_desc[t];
             if (a.wts_out) a.wts_out[(size_t)li * NU + t] = ctl->p_desc[t];
         }
-        quant_vec(FFS, s.q_hd, s.s_hd, s.c_hd, [&](int i) { return ll_read(a.x_hd + i, epoch, ctl, a.status); });
-        cons_sync();
         STAMP(li, 4);
         /* ---------------- D: shared down rows + routed gate|up pairs ---------------- */
         {
             const int n32 = E >> 5, n32s = FFS >> 5;
-            const Act act_in{reinterpret_cast<const int4 *>(s.q_in), s.s_in, s.c_in};
-            const Act act_hd{reinterpret_cast<const int4 *>(s.q_hd), s.s_hd, s.c_hd};
             {
-                PairWalk w(g.j0, g.nj, 1 << 30, g.RS, cid);
-                for (int j = g.j0 + warp; j < g.j0 + g.nj; j += kCW) {
-                    while (j >= w.end()) { C.release(w.cid); w.next(); }
-                    const unsigned char *base = C.wait(w.cid);
-                    const int n = w.end() - w.pos, idx = j - w.pos;
-                    const unsigned dl = (unsigned)((uintptr_t)((const unsigned char *)L.sd_bs + (size_t)w.pos * g.sbS) & 15);
-                    const float o = row_dot(base + (size_t)idx * g.rbS, base + (size_t)n * g.rbS + dl + (size_t)idx * g.sbS, n32s, lane, act_hd);
-                    if (lane == 0) ll_write(a.x_dn + j, o, epoch);
+                constexpr int R = 2;
+                const Act act_hd{reinterpret_cast<const int4 *>(s.q_hd), s.s_hd, s.c_hd};
+                SegWalk w(g.j0, g.nj, 1 << 30, g.RS, ring);
+                const int jend = g.j0 + g.nj;
+#pragma unroll 1
+                for (int j0 = g.j0 + warp * R; j0 < jend; j0 += kCW * R) {
+                    const unsigned char *codes[R], *scales[R]; const Act acts[R] = {act_hd, act_hd};
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const int j = (j0 + r < jend) ? j0 + r : j0;
+                        while (j >= w.end()) { C.release(w.r); w.next(); }
+                        const unsigned char *base = C.wait(w.r);
+                        const int n = w.end() - w.pos, idx = j - w.pos;
+                        const unsigned dl = (unsigned)((uintptr_t)((const unsigned char *)L.sd_bs + (size_t)w.pos * g.sbS) & 15);
+                        codes[r] = base + (size_t)idx * g.rbS; scales[r] = base + (size_t)n * g.rbS + dl + (size_t)idx * g.sbS;
+                    }
+                    float o[R];
+                    rows_dot<NIT_S, R>(codes, scales, acts, n32s, lane, o);
+                    if (lane == 0) {
+#pragma unroll
+                        for (int r = 0; r < R; r++) if (j0 + r < jend) ll_write(a.x_dn + j0 + r, o[r], epoch);
+                    }
                 }
-                while (w.valid()) { C.release(w.cid); w.next(); }
-                cid = w.cid;
+                while (w.valid()) { C.release(w.r); w.next(); }
+                ring = w.r;
             }
+            STAMP(li, 14);
             {
-                PairWalk w(g.P0, g.nP, FFE, g.PB, cid);
-                for (int pu = g.P0 + warp; pu < g.P0 + g.nP; pu += kCW) {
-                    while (pu >= w.end()) { C.release(w.cid); w.next(); }
-                    const unsigned char *base = C.wait(w.cid);
-                    const int n = w.end() - w.pos, idx = pu - w.pos;
-                    const int slot = w.pos / FFE, c = w.pos - slot * FFE;
-                    const size_t grow = (size_t)ctl->sel_asc[slot] * 2 * FFE + c, urow = grow + FFE;
-                    const unsigned cb = (unsigned)(n * g.rbE), sr = (unsigned)sr_bytes(n, g.sbE);
-                    const unsigned dg = (unsigned)((uintptr_t)((const unsigned char *)L.gu_bs + grow * g.sbE) & 15);
-                    const unsigned du = (unsigned)((uintptr_t)((const unsigned char *)L.gu_bs + urow * g.sbE) & 15);
-                    const float h = pair_dot_gelu(base + (size_t)idx * g.rbE, base + 2 * cb + dg + (size_t)idx * g.sbE,
-                                                  base + cb + (size_t)idx * g.rbE, base + 2 * cb + sr + du + (size_t)idx * g.sbE, n32, lane, act_in);
-                    if (lane == 0) ll_write(a.x_h + pu, h, epoch);
+                SegWalk w(g.P0, g.nP, FFE, g.PB, ring);
+#ifdef SP_DECODE_STAMPS
+                if (t == 0 && g.nP > 0) { C.wait(ring); STAMP(li, 13); }
+#endif
+                const int Pend = g.P0 + g.nP;
+#pragma unroll 1
+                for (int q0 = g.P0 + warp * 2; q0 < Pend; q0 += kCW * 2) {
+                    PairPtrs pp[2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        const int pu = (q0 + r < Pend) ? q0 + r : q0;
+                        while (pu >= w.end()) { C.release(w.r); w.next(); }
+                        const unsigned char *base = C.wait(w.r);
+                        const int n = w.end() - w.pos, idx = pu - w.pos;
+                        const size_t grow = (size_t)ctl->sel_asc[w.seg] * 2 * FFE + w.seg_off(), urow = grow + FFE;
+                        const unsigned cb = (unsigned)(n * g.rbE), sr = (unsigned)sr_bytes(n, g.sbE);
+                        const unsigned dg = (unsigned)((uintptr_t)((const unsigned char *)L.gu_bs + grow * g.sbE) & 15);
+                        const unsigned du = (unsigned)((uintptr_t)((const unsigned char *)L.gu_bs + urow * g.sbE) & 15);
+                        pp[r] = PairPtrs{base + (size_t)idx * g.rbE, base + 2 * cb + dg + (size_t)idx * g.sbE,
+                                         base + cb + (size_t)idx * g.rbE, base + 2 * cb + sr + du + (size_t)idx * g.sbE};
+                    }
+                    const float2 h = pairs2_gelu<NIT_E>(pp[0], pp[1], reinterpret_cast<const int4 *>(s.q_in), s.s_in, s.c_in, n32, lane);
+                    if (lane == 0) { ll_write(a.x_h + q0, h.x, epoch); if (q0 + 1 < Pend) ll_write(a.x_h + q0 + 1, h.y, epoch); }
                 }
-                while (w.valid()) { C.release(w.cid); w.next(); }
-                cid = w.cid;
+                while (w.valid()) { C.release(w.r); w.next(); }
+                ring = w.r;
             }
         }
         STAMP(li, 5);
-        /* the element-wise vectors of G (this layer) and A (next layer): fetched now, used after F */
+        /* ---------------- E: quantise the expert activations ---------------- */
+#pragma unroll 1
+        for (int bq = t; bq < ((NU * FFE) >> 4); bq += kCons)
+            ll_quant16(a.x_h + 16 * bq, epoch, reinterpret_cast<int4 *>(s.q_h) + bq, s.s_h + bq, s.c_h + bq, ctl, a.status);
+        cons_sync();
+        STAMP(li, 6);
+        /* ---------------- F: routed down rows + ordered combine ---------------- */
         {
+            constexpr int R = 4;
+            const int n32 = FFE >> 5, blk16 = FFE >> 4, U = NU * g.nj;
+            FWalk w(g, NU, ring);
+            /* unit u = slot*nj + jj, walked without division */
+            int slot = 0, jj = warp * R;
+            while (jj >= g.nj && slot < NU) { jj -= g.nj; slot++; }
+#pragma unroll 1
+            for (int u0 = warp * R; u0 < U; u0 += kCW * R) {
+                const unsigned char *codes[R], *scales[R]; Act acts[R]; int oslot[R], ojj[R];
+                int sl = slot, j = jj;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const bool live = u0 + r < U;
+                    const int us = live ? sl : slot, uj = live ? j : jj;
+                    oslot[r] = live ? us : -1; ojj[r] = uj;
+                    while (!w.holds(us, uj)) { C.release(w.r); w.next(); }
+                    const unsigned char *base = C.wait(w.r);
+                    const int rows = w.rf();
+                    const unsigned cb = (unsigned)(rows * g.rbF);
+                    const unsigned blk = cb + (unsigned)sr_bytes(rows, g.sbF);
+                    const unsigned char *xb = base + (size_t)(us - w.s) * blk;
+                    const size_t row_first = (size_t)ctl->sel_asc[us] * E + g.j0 + w.jr;
+                    const unsigned dl = (unsigned)((uintptr_t)((const unsigned char *)L.dn_bs + row_first * g.sbF) & 15);
+                    const int idx = uj - w.jr;
+                    codes[r] = xb + (size_t)idx * g.rbF; scales[r] = xb + cb + dl + (size_t)idx * g.sbF;
+                    acts[r] = Act{reinterpret_cast<const int4 *>(s.q_h) + (size_t)us * blk16, s.s_h + (size_t)us * blk16, s.c_h + (size_t)us * blk16};
+                    if (++j == g.nj) { j = 0; sl++; }
+                }
+                float o[R];
+                rows_dot<NIT_F, R>(codes, scales, acts, n32, lane, o);
+                if (lane == 0) {
+#pragma unroll
+                    for (int r = 0; r < R; r++) if (oslot[r] >= 0) s.out[oslot[r] * rows_f_max + ojj[r]] = o[r];
+                }
+                jj += kCW * R;
+                while (jj >= g.nj && slot < NU) { jj -= g.nj; slot++; }
+            }
+            while (w.valid()) { C.release(w.r); w.next(); }
+            ring = w.r;
+            cons_sync();
+#pragma unroll 1
+            for (int q = t; q < g.nj; q += kCons) {                      /* k_moe_combine_ord, CF:6071-6077 */
+                float acc = 0.0f;
+                for (int k = 0; k < NU; k++) acc = __fadd_rn(acc, __fmul_rn(ctl->cw[k], s.out[k * rows_f_max + q]));
+                ll_write(a.x_acc + g.j0 + q, acc, epoch);
+            }
+        }
+        STAMP(li, 7);
+        /* ---------------- G: recombine (CF:9014-9019), on this thread's own elements ---------------- */
+        {
+            /* this layer's output norms and the next layer's input norms: requested before the poll
+             * below, so their latency hides behind it */
+            float w1[KE], w2[KE], w3[KE];
             const bool more = li + 1 < a.n_layers;
-            const SpLayerDev &Ln = a.layers[a.layer_first + li + (more ? 1 : 0)];
+            const SpLayerDev Ln = layer_at(a, li + (more ? 1 : 0));
 #pragma unroll
             for (int k = 0; k < KE; k++) {
                 const int i = t + kCons * k;
+                w1[k] = w2[k] = w3[k] = 0.0f;
                 if (i < E) {
                     w1[k] = __ldg(L.post_ffw1 + i); w2[k] = __ldg(L.post_ffw2 + i); w3[k] = __ldg(L.post_ffw + i);
                     if (more) { wn[k] = __ldg(Ln.ffn_norm + i); wp[k] = __ldg(Ln.pre_ffw2 + i); rs[k] = __ldg(Ln.router_scale + i); }
                 }
             }
-        }
-        /* ---------------- E: quantise the expert activations ---------------- */
-        quant_vec(NU * FFE, s.q_h, s.s_h, s.c_h, [&](int i) { return ll_read(a.x_h + i, epoch, ctl, a.status); });
-        cons_sync();
-        STAMP(li, 6);
-        /* ---------------- F: routed down rows + ordered combine ---------------- */
-        {
-            const int n32 = FFE >> 5, blk16 = FFE >> 4;
-            FWalk w(g, NU, cid);
-            for (int u = warp; u < NU * g.nj; u += kCW) {
-                while (u >= w.end()) { C.release(w.cid); w.next(); }
-                const unsigned char *base = C.wait(w.cid);
-                const int slot = u / g.nj, jj = u - slot * g.nj;
-                const int s0 = w.u / g.nj, jr0 = w.u - s0 * g.nj;
-                const bool whole = g.RF == g.nj;
-                const int rows = whole ? g.nj : (w.end() - w.u);
-                const unsigned cb = (unsigned)(rows * g.rbF);
-                const unsigned blk = cb + (unsigned)sr_bytes(rows, g.sbF);
-                const unsigned char *xb = base + (size_t)(slot - s0) * blk;
-                const size_t row_first = (size_t)ctl->sel_asc[slot] * E + g.j0 + (whole ? 0 : jr0);
-                const unsigned dl = (unsigned)((uintptr_t)((const unsigned char *)L.dn_bs + row_first * g.sbF) & 15);
-                const int idx = whole ? jj : (jj - jr0);
-                const Act act{reinterpret_cast<const int4 *>(s.q_h) + (size_t)slot * blk16, s.s_h + (size_t)slot * blk16, s.c_h + (size_t)slot * blk16};
-                const float o = row_dot(xb + (size_t)idx * g.rbF, xb + cb + dl + (size_t)idx * g.sbF, n32, lane, act);
-                if (lane == 0) s.out[slot * rows_f_max + jj] = o;
-            }
-            while (w.valid()) { C.release(w.cid); w.next(); }
-            cid = w.cid;
-            cons_sync();
-            for (int jj = t; jj < g.nj; jj += kCons) {                   /* k_moe_combine_ord, CF:6071-6077 */
-                float acc = 0.0f;
-                for (int k = 0; k < NU; k++) acc = __fadd_rn(acc, __fmul_rn(ctl->cw[k], s.out[k * rows_f_max + jj]));
-                ll_write(a.x_acc + g.j0 + jj, acc, epoch);
-            }
-        }
-        STAMP(li, 7);
-        /* ---------------- G: recombine (CF:9014-9019) ---------------- */
-        {
-            for (int i = t; i < E; i += kCons) { s.va[i] = ll_read(a.x_dn + i, epoch, ctl, a.status); s.vb[i] = ll_read(a.x_acc + i, epoch, ctl, a.status); }
-            cons_sync();
-            const float sc1 = rms_scale_from(block_sumsq(s.va, E, s.red), E, d.eps);
-            const float sc2 = rms_scale_from(block_sumsq(s.vb, E, s.red), E, d.eps);
+            float dnv[KE], acv[KE];
+#pragma unroll 1
+            for (unsigned spins = 0;; spins++) {                        /* all loads in flight together */
+                bool ok = true;
 #pragma unroll
-            for (int k = 0; k < KE; k++) {
-                const int i = t + kCons * k;
-                if (i < E) {
-                    const float mlp = __fmul_rn(__fmul_rn(s.va[i], sc1), w1[k]);
-                    const float t1 = __fmul_rn(__fmul_rn(s.vb[i], sc2), w2[k]);
-                    s.va[i] = __fadd_rn(mlp, t1);
+                for (int k = 0; k < KE; k++) {
+                    const int i = t + kCons * k;
+                    dnv[k] = 0.0f; acv[k] = 0.0f;
+                    if (i < E) {
+                        const unsigned long long wd = ld_relaxed_u64(a.x_dn + i), wa = ld_relaxed_u64(a.x_acc + i);
+                        ok = ok && ((unsigned)(wd >> 32) == epoch) && ((unsigned)(wa >> 32) == epoch);
+                        dnv[k] = __uint_as_float((unsigned)wd); acv[k] = __uint_as_float((unsigned)wa);
+                    }
                 }
+                if (ok) break;
+                if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) break;
+                if (spins > kSpinLimit) { *(volatile int *)&ctl->abort = 1; atomicExch(a.status, SP_KERR_BARRIER_TIMEOUT); break; }
             }
+            STAMP(li, 11);
+            double p1 = 0.0, p2 = 0.0;
+#pragma unroll
+            for (int k = 0; k < KE; k++) { const double u = dnv[k], v = acv[k]; p1 += u * u; p2 += v * v; }
+            /* two sums, one barrier */
+            p1 = warp_sum_f64(p1); p2 = warp_sum_f64(p2);
+            if (lane == 0) { s.red[16 + warp] = p1; s.red[32 + warp] = p2; }
             cons_sync();
-            const float sc3 = rms_scale_from(block_sumsq(s.va, E, s.red), E, d.eps);
+            double ss1 = 0.0, ss2 = 0.0;
+#pragma unroll
+            for (int w = 0; w < kCW; w++) { ss1 += s.red[16 + w]; ss2 += s.red[32 + w]; }
+            const float sc1 = rms_scale_from(ss1, E, d.eps), sc2 = rms_scale_from(ss2, E, d.eps);
+            double p3 = 0.0;
 #pragma unroll
             for (int k = 0; k < KE; k++) {
-                const int i = t + kCons * k;
-                if (i < E) s.x[i] = __fadd_rn(s.x[i], __fmul_rn(__fmul_rn(s.va[i], sc3), w3[k]));
+                const float mlp = __fmul_rn(__fmul_rn(dnv[k], sc1), w1[k]);
+                const float t1 = __fmul_rn(__fmul_rn(acv[k], sc2), w2[k]);
+                dnv[k] = __fadd_rn(mlp, t1);
+                const double v = dnv[k]; p3 += v * v;
             }
-            cons_sync();
+            const float sc3 = rms_scale_from(block_sum(p3, s.red + 48), E, d.eps);
+#pragma unroll
+            for (int k = 0; k < KE; k++) xr[k] = __fadd_rn(xr[k], __fmul_rn(__fmul_rn(dnv[k], sc3), w3[k]));
         }
     }
-    if (b == 0) for (int i = t; i < E; i += kCons) a.y_out[i] = s.x[i];
+    if (b == 0) {
+#pragma unroll
+        for (int k = 0; k < KE; k++) { const int i = t + kCons * k; if (i < E) a.y_out[i] = xr[k]; }
+    }
 }
 
 }  // namespace
 
 int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_bytes) {
     const int rows_f_max = (d.E + grid - 1) / grid + 1;
-    const size_t fixed = smem_layout(d, rows_f_max, [](int, size_t) {});
+    const size_t fixed = smem_layout(d, rows_f_max).ring;
     if (fixed + 2 * (size_t)kSlot > smem_limit) { *smem_bytes = 0; return 0; }
     size_t ns = (smem_limit - fixed) / kSlot;
     if (ns > (size_t)kMaxSlots) ns = kMaxSlots;
@@ -739,11 +914,19 @@ int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_b
 }
 int sp_decode_threads() { return kThreads; }
 
-cudaError_t sp_decode_prepare(size_t smem, int *max_grid) {
-    cudaError_t e = cudaFuncSetAttribute(k_moe_decode_stack, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static const void *decode_kernel(const SpDims &d) {
+    /* the Gemma-4-26B-A4B geometry gets its own instantiation; everything else the general one */
+    return (d.E <= 6 * kCons && d.E <= 3 * 1024 && d.FFS <= 3 * 1024 && d.FFE <= 1024)
+               ? (const void *)k_moe_decode_stack<6, 3, 3, 1> : (const void *)k_moe_decode_stack<9, 4, 4, 4>;
+}
+
+cudaError_t sp_decode_prepare(const SpDims &d, size_t smem, int *max_grid) {
+    if (d.E > 9 * kCons) return cudaErrorInvalidValue;
+    const void *fn = decode_kernel(d);
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     int per_sm = 0, dev = 0, sms = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_moe_decode_stack, kThreads, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, smem);
     if (e != cudaSuccess) return e;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -754,5 +937,5 @@ cudaError_t sp_decode_prepare(size_t smem, int *max_grid) {
 cudaError_t sp_decode_launch(const SpDecodeArgs &args, int grid, size_t smem, cudaStream_t st) {
     SpDecodeArgs a = args;
     void *params[] = {&a};
-    return cudaLaunchCooperativeKernel((const void *)k_moe_decode_stack, dim3(grid), dim3(kThreads), params, smem, st);
+    return cudaLaunchCooperativeKernel(decode_kernel(args.d), dim3(grid), dim3(kThreads), params, smem, st);
 }

@@ -3,7 +3,9 @@
 #include "common.cuh"
 
 struct SpDecodeArgs {
-    const SpLayerDev *layers;      /* device array of all layers */
+    SpLayerDev layer0;             /* device pointers of layer 0 (router_bias always set: see bias_mask) */
+    size_t layer_stride;           /* bytes between consecutive layers' slabs */
+    unsigned long long bias_mask;  /* bit li: layer layer_first + li has a router bias (n_layers <= 64 per launch) */
     int layer_first, n_layers;
     SpDims d;
     const float *x_in;             /* [E] */
@@ -25,5 +27,5 @@ struct SpDecodeArgs {
 /* ring slots and total dynamic shared memory for these dims under `smem_limit`; 0 if it cannot fit */
 int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_bytes);
 int sp_decode_threads();
-cudaError_t sp_decode_prepare(size_t smem, int *max_grid);
+cudaError_t sp_decode_prepare(const SpDims &d, size_t smem, int *max_grid);
 cudaError_t sp_decode_launch(const SpDecodeArgs &args, int grid, size_t smem, cudaStream_t st);
