@@ -47,7 +47,7 @@ typedef struct sp_moe sp_moe;          /* opaque; replaces the engine-owned g_w 
 #define SP_MOE_FLAVOUR_PREFILL 1   /* exact Q4B dequant, floating-point GEMM (prefill, M large) */
 
 typedef struct {
-    int32_t E;           /* hidden size; multiple of 32, <= 8192 */
+    int32_t E;           /* hidden size; multiple of 32, <= 4096 */
     int32_t NE;          /* routed experts per layer, <= 1024 */
     int32_t NU;          /* experts used per token, <= 8 (G4G_MAX, CF:5989) */
     int32_t FFE;         /* routed expert FFN width; multiple of 32 */
@@ -123,6 +123,13 @@ int sp_moe_q4b_quantize_dev(const float *w_dev, int64_t rows, int cols,
 /* k_dequant_arena_q4b, CF:1452-1464. */
 int sp_moe_q4b_dequantize_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int64_t rows, int cols,
                               float *w_dev, void *stream);
+
+/* gemv_w_packed for OK_Q4B (CF:13566-13599): y[rows] = W . x in the decode arithmetic (int8 per-16
+ * activation quant, CF:1564-1585, then the Q4B x int8 GEMV, CF:1688-1713). DEVICE pointers; W is
+ * [rows][in/2] codes + f16 [rows][in/32] scales; in a multiple of 32, at most 4096. Allocates its int8
+ * scratch for the call, synchronises the stream and frees it. */
+int sp_moe_gemv_q4b_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int in, int rows,
+                        const float *x_dev, float *y_dev, void *stream);
 
 /* k_gelu_mul (CF:1364-1373): out[i] = gelu_tanh(g[i]) * up[i] on DEVICE memory, in the library's
  * bit-reproducible arithmetic (the tanh is a fixed sequence of correctly-rounded operations). */

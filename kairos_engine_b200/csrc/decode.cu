@@ -58,6 +58,9 @@ constexpr int kThreads = kCons + 32;       /* + one producer warp = 16 warps: 4 
 constexpr int kSlot = 16384;               /* ring slot bytes */
 constexpr int kMaxSlots = 12;
 constexpr unsigned kSpinLimit = 1u << 22;  /* polls before a wait gives up (order of a second) */
+constexpr int kMaxInFlight = 4;            /* chunks the producer keeps in flight: enough for full HBM rate (measured), while a
+                                              deeper queue only delays the small exchange loads that share the memory system */
+constexpr unsigned kPollNs = 128;          /* pause between polls of another CTA's word: polling must not flood L2 */
 
 /* ---------------------------------------------------------------- PTX helpers */
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -234,6 +237,7 @@ __device__ __noinline__ float ll_read(const unsigned long long *p, unsigned epoc
     for (unsigned spins = 0; spins < kSpinLimit; spins++) {
         const unsigned long long v = ld_relaxed_u64(p);
         if ((unsigned)(v >> 32) == epoch) return __uint_as_float((unsigned)v);
+        __nanosleep(kPollNs);
         if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) return 0.0f;
     }
     *(volatile int *)&ctl->abort = 1;
@@ -259,8 +263,10 @@ __device__ __forceinline__ double block_sum(double v, double *sh) {
     for (int w = 0; w < kCW; w++) r += sh[w];
     return r;
 }
-__device__ __noinline__ float rms_scale_from(double ss, int n, float eps) {
-    const float ms = (float)(ss / (double)n);
+/* mean of squares -> 1/sqrt(ms + eps). The mean is ss * (1/n) in double (the reference divides,
+ * CF:511; the two differ at most in the last bit of a double that is rounded to float next). */
+__device__ __noinline__ float rms_scale_from(double ss, double inv_n, float eps) {
+    const float ms = (float)(ss * inv_n);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
 }
 __device__ __noinline__ float gelu_mul_ni(float g, float u) { return gelu_mul(g, u); }
@@ -348,6 +354,7 @@ __device__ __forceinline__ float router_row(const float *wrow, const float *rin,
  * matches) and quantise them as one block. Out of line: it is big and has two callers. */
 __device__ __noinline__ void ll_quant16(const unsigned long long *p, unsigned epoch, int4 *dst, float *sx, int *corr, Ctl *ctl, int *status) {
     float v[16];
+    (void)ll_read(p, epoch, ctl, status);              /* wait on ONE word first; the other 15 follow closely */
     for (unsigned spins = 0; spins < kSpinLimit; spins++) {
         unsigned long long w[16];
 #pragma unroll
@@ -356,6 +363,7 @@ __device__ __noinline__ void ll_quant16(const unsigned long long *p, unsigned ep
 #pragma unroll
         for (int i = 0; i < 16; i++) { ok = ok && ((unsigned)(w[i] >> 32) == epoch); v[i] = __uint_as_float((unsigned)w[i]); }
         if (ok) break;
+        __nanosleep(kPollNs);
         if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) break;
         if (spins == kSpinLimit - 1) { *(volatile int *)&ctl->abort = 1; atomicExch(status, SP_KERR_BARRIER_TIMEOUT); }
     }
@@ -388,6 +396,7 @@ __device__ __noinline__ void topk_warps(const SpDecodeArgs &a, const SpDims &d, 
     if (bad && (t & 31) == 0) atomicExch(a.status, SP_KERR_NAN_ROUTER);
     if (t < SP_MAX_NU) { ctl->sel_desc[t] = t < NE ? t : 0; ctl->p_desc[t] = 0.0f; }
     tsync();
+    STAMP(epoch - a.epoch_base - 1, 3);
     mx = wmaxf[0];
     for (int w = 1; w < tw; w++) mx = fmaxf(mx, wmaxf[w]);
     /* exp in double, summed in double in a fixed order (strided partials, shuffle tree, warps in order) */
@@ -400,7 +409,8 @@ __device__ __noinline__ void topk_warps(const SpDecodeArgs &a, const SpDims &d, 
     double sum = 0.0;
     for (int w = 0; w < tw; w++) sum += wsum[w];
 #pragma unroll 1
-    for (int i = t; i < NE; i += T) s.p[i] = (float)(s.ex[i] / sum);
+    const double rsum = 1.0 / sum;                         /* one division; p = e * (1/sum) rounded to float */
+    for (int i = t; i < NE; i += T) s.p[i] = (float)(s.ex[i] * rsum);
     tsync();
     /* insertion with strict > == rank by (p desc, id asc) */
 #pragma unroll 1
@@ -459,8 +469,12 @@ __device__ __forceinline__ SpLayerDev layer_at(const SpDecodeArgs &a, int li) {
 
 /* ---------------------------------------------------------------- the producer warp's lane */
 struct Producer {
-    Ctl *ctl; unsigned char *ring; Ring r; int *status; bool ok; int issued;
+    Ctl *ctl; unsigned char *ring; Ring r; int *status; bool ok; int issued; Ring lag;
     __device__ unsigned char *acquire() {
+        if (issued >= kMaxInFlight && ok) {                 /* chunk (issued - kMaxInFlight) must have landed */
+            ok = wait_bar(&ctl->full[lag.slot], lag.par, ctl, status, 32);
+            lag.adv();
+        }
         if (r.wrapped && ok) ok = wait_bar(&ctl->empty[r.slot], r.par ^ 1u, ctl, status, 64);
         return ring + (size_t)r.slot * kSlot;
     }
@@ -472,7 +486,7 @@ struct Producer {
         asrc = src - delta;
         return (delta + (unsigned)nbytes + 15u) & ~15u;
     }
-    __device__ void pairs(const unsigned char *gc, const unsigned char *gs, const unsigned char *uc, const unsigned char *us, int n, int rb, int sb) {
+    __device__ __noinline__ void pairs(const unsigned char *gc, const unsigned char *gs, const unsigned char *uc, const unsigned char *us, int n, int rb, int sb) {
         unsigned char *dst = acquire();
         if (ok) {
             const unsigned char *ags, *aus;
@@ -486,7 +500,7 @@ struct Producer {
         }
         done();
     }
-    __device__ void rows(const unsigned char *c, const unsigned char *sc, int n, int rb, int sb) {
+    __device__ __noinline__ void rows(const unsigned char *c, const unsigned char *sc, int n, int rb, int sb) {
         unsigned char *dst = acquire();
         if (ok) {
             const unsigned char *as;
@@ -497,7 +511,7 @@ struct Producer {
         }
         done();
     }
-    __device__ void rows2(const unsigned char *c0, const unsigned char *s0, const unsigned char *c1, const unsigned char *s1, int n, int rb, int sb) {
+    __device__ __noinline__ void rows2(const unsigned char *c0, const unsigned char *s0, const unsigned char *c1, const unsigned char *s1, int n, int rb, int sb) {
         unsigned char *dst = acquire();
         if (ok) {
             const unsigned char *a0, *a1;
@@ -511,7 +525,7 @@ struct Producer {
         }
         done();
     }
-    __device__ void flat(const void *src, unsigned bytes) {
+    __device__ __noinline__ void flat(const void *src, unsigned bytes) {
         unsigned char *dst = acquire();
         if (ok) { mbar_expect_tx(bar(), bytes); bulk_g2s(dst, src, bytes, bar()); }
         done();
@@ -520,7 +534,7 @@ struct Producer {
 
 __device__ __noinline__ void producer_main(const SpDecodeArgs &a, const Geo &g, Smem &s, int ns) {
     const SpDims &d = a.d;
-    Producer P{s.ctl, s.ring, Ring{0, ns, 0u, false}, a.status, true, 0};
+    Producer P{s.ctl, s.ring, Ring{0, ns, 0u, false}, a.status, true, 0, Ring{0, ns, 0u, false}};
     const Ring nil{0, 1, 0u, false};
 #pragma unroll 1
     for (int li = 0; li < a.n_layers; li++) {
@@ -610,6 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
 
     /* ---------------------------------------------------------------- consumers */
     Consumer C{ctl, s.ring, a.status, lane};
+    const double inv_n = 1.0 / (double)E;
     Ring ring{0, ns, 0u, false};                         /* next chunk to consume */
     const int tw = ((NE + 31) / 32 < 4) ? 4 : (((NE + 31) / 32 > kCW) ? kCW : (NE + 31) / 32);   /* warps that run the top-k */
     /* the residual and the norm / scale vectors of the element-wise steps ride in registers:
@@ -638,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
             double part = 0.0;
 #pragma unroll
             for (int k = 0; k < KE; k++) { const double v = xr[k]; part += v * v; }      /* elements past E are 0 */
-            const float scale = rms_scale_from(block_sum(part, s.red), E, d.eps);
+            const float scale = rms_scale_from(block_sum(part, s.red), inv_n, d.eps);
             STAMP(li, 8);
 #pragma unroll
             for (int k = 0; k < KE; k++) {
@@ -853,6 +868,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
                 }
             }
             float dnv[KE], acv[KE];
+            (void)ll_read(a.x_acc + (t < E ? t : 0), epoch, ctl, a.status);   /* wait on ONE word first */
 #pragma unroll 1
             for (unsigned spins = 0;; spins++) {                        /* all loads in flight together */
                 bool ok = true;
@@ -867,6 +883,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
                     }
                 }
                 if (ok) break;
+                __nanosleep(kPollNs);
                 if ((spins & 63) == 63 && *(volatile int *)&ctl->abort) break;
                 if (spins > kSpinLimit) { *(volatile int *)&ctl->abort = 1; atomicExch(a.status, SP_KERR_BARRIER_TIMEOUT); break; }
             }
@@ -881,7 +898,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
             double ss1 = 0.0, ss2 = 0.0;
 #pragma unroll
             for (int w = 0; w < kCW; w++) { ss1 += s.red[16 + w]; ss2 += s.red[32 + w]; }
-            const float sc1 = rms_scale_from(ss1, E, d.eps), sc2 = rms_scale_from(ss2, E, d.eps);
+            const float sc1 = rms_scale_from(ss1, inv_n, d.eps), sc2 = rms_scale_from(ss2, inv_n, d.eps);
             double p3 = 0.0;
 #pragma unroll
             for (int k = 0; k < KE; k++) {
@@ -890,7 +907,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_moe_decode_stack(SpDecodeArgs a
                 dnv[k] = __fadd_rn(mlp, t1);
                 const double v = dnv[k]; p3 += v * v;
             }
-            const float sc3 = rms_scale_from(block_sum(p3, s.red + 48), E, d.eps);
+            const float sc3 = rms_scale_from(block_sum(p3, s.red + 48), inv_n, d.eps);
 #pragma unroll
             for (int k = 0; k < KE; k++) xr[k] = __fadd_rn(xr[k], __fmul_rn(__fmul_rn(dnv[k], sc3), w3[k]));
         }

@@ -159,3 +159,28 @@ extern "C" int gemma4_moe_ffn_q4b_cuda(int E, int NE, int NU, int FF, float eps,
 #undef SA
     return 0;
 }
+
+/* gemv_w_packed for OK_Q4B (CF:13566-13599): y[rows] = Q4B(W)[rows][in] . x[in] in the decode
+ * arithmetic: k_quant_act_int8 on x (CF:1564-1585), then k_gemv_q4b_dp4a_v2 (CF:1688-1713).
+ * Device pointers. The reference's caller owns the int8 scratch (dqx, dsx); here the call
+ * allocates it and frees it again. */
+extern "C" int sp_moe_gemv_q4b_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int in, int rows,
+                                   const float *x_dev, float *y_dev, void *stream) {
+    if (!codes_dev || !bs_dev || !x_dev || !y_dev || in <= 0 || rows <= 0 || (in & 31) || in > 4096) {     /* gemv_w_packed declines in % 32 != 0, CF:13574 */
+        sp_set_error("sp_moe_gemv_q4b_dev: bad argument (in must be a multiple of 32, at most 4096)"); return SP_MOE_EBADARG; }
+    cudaStream_t st = (cudaStream_t)stream;
+    signed char *q = nullptr; float *sx = nullptr; int *corr = nullptr;
+    cudaError_t e = cudaMalloc(&q, (size_t)in);
+    if (e == cudaSuccess) e = cudaMalloc(&sx, sizeof(float) * (in / 16));
+    if (e == cudaSuccess) e = cudaMalloc(&corr, sizeof(int) * (in / 16));
+    if (e == cudaSuccess) {
+        k_sa_quant<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
+        k_sa_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);            /* the scratch is freed below */
+    }
+    cudaFree(q); cudaFree(sx); cudaFree(corr);
+    if (e != cudaSuccess) { char b[256]; snprintf(b, sizeof b, "sp_moe_gemv_q4b_dev: %s", cudaGetErrorString(e)); sp_set_error(b); cudaGetLastError();
+        return e == cudaErrorMemoryAllocation ? SP_MOE_EBACKEND_OOM : SP_MOE_ECUDA; }
+    return SP_MOE_OK;
+}

@@ -130,3 +130,14 @@ def gelu_mul(g, up):
     check(_lib.lib().sp_moe_gelu_mul_dev(g.data_ptr(), up.data_ptr(), g.numel(), out.data_ptr(),
                                          torch.cuda.current_stream(g.device).cuda_stream))
     return out
+
+
+def gemv_q4b(codes, bs, x):
+    """torch CUDA tensors: codes uint8 [rows][in/2], bs int16 [rows][in/32], x f32 [in] -> y f32 [rows]
+    (gemv_w_packed of the reference: int8 activation quant + Q4B x int8 GEMV)."""
+    import torch
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    y = torch.empty(rows, dtype=torch.float32, device=codes.device)
+    check(_lib.lib().sp_moe_gemv_q4b_dev(codes.data_ptr(), bs.data_ptr(), cols, rows, x.contiguous().data_ptr(), y.data_ptr(),
+                                         torch.cuda.current_stream(codes.device).cuda_stream))
+    return y

@@ -100,3 +100,17 @@ def test_gelu_is_bit_identical_to_checker():
     L = orc.lib()
     ref = np.array([L.orc_gelu_mul(float(a), float(b)) for a, b in zip(xs[::7], us[::7])], np.float32)
     assert np.array_equal(got[::7].view(np.uint32), ref.view(np.uint32))
+
+
+def test_gemv_q4b_entry_matches_checker_bitwise():
+    import torch
+    from kairos_engine_b200 import gemv_q4b, q4b_quantize
+    g = torch.Generator(device="cuda").manual_seed(9)
+    for rows, cols in ((1408, 2816), (2816, 704), (33, 64)):
+        w = torch.randn((rows, cols), generator=g, device="cuda") * 0.02
+        codes, bs = q4b_quantize(w)
+        x = torch.randn(cols, generator=g, device="cuda")
+        y = gemv_q4b(codes, bs, x).cpu().numpy()
+        qx, sx = orc.quant_act(x.cpu().numpy())
+        ref = orc.gemv_a(codes.cpu().numpy(), bs.cpu().numpy().view(np.uint16), rows, cols, qx, sx)
+        assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
