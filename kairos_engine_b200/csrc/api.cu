@@ -15,6 +15,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <cstdlib>
 #include <vector>
 
 /* ---------------------------------------------------------------- error text (sp_status.h:57-59) */
@@ -62,6 +63,12 @@ struct sp_moe {
     /* host-pointer entry staging */
     float *x_dev, *y_dev; int32_t *sel_dev; float *wts_dev;
     SpBatchedScratch bs;
+    /* three-kernel decode path replayed from CUDA graphs, one per (first layer, layer count) */
+    struct DecodeGraph { int lf, nl; bool routing; cudaGraphExec_t exec; int launches; };
+    std::vector<DecodeGraph> graphs;
+    SpGraphScratch gs; unsigned char *gs_base; float *g_x, *g_y; int32_t *g_sel; float *g_wts;
+    int decode_impl;            /* 0 = CUDA graph of three kernels per layer, 1 = one persistent kernel */
+    int sms;
     cudaStream_t stream;        /* stream of the host-pointer entry */
     cudaStream_t last_stream;
     size_t scratch_bytes;
@@ -145,6 +152,25 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     const size_t mt = (size_t)c.max_tokens;
     OPEN_CK(dalloc((void **)&h->x_dev, 4 * mt * c.E), "staging"); OPEN_CK(dalloc((void **)&h->y_dev, 4 * mt * c.E), "staging");
     OPEN_CK(dalloc((void **)&h->sel_dev, 4 * mt * c.NU * c.n_layers), "staging"); OPEN_CK(dalloc((void **)&h->wts_dev, 4 * mt * c.NU * c.n_layers), "staging");
+    {   /* scratch of the graph decode path */
+        const size_t E = c.E, NE = c.NE, NU = c.NU, FFE = c.FFE, FFS = c.FFS;
+        size_t o = 0; auto take = [&](size_t bytes) { size_t at = o; o = up256(o + bytes); return at; };
+        const size_t o_lg = take(4 * NE), o_hd = take(4 * FFS), o_dn = take(4 * E), o_h = take(4 * NU * FFE), o_acc = take(4 * E),
+                     o_q = take(E), o_s = take(4 * (E / 16)), o_c = take(4 * (E / 16)), o_sel = take(4 * SP_MAX_NU), o_cw = take(4 * SP_MAX_NU),
+                     o_x0 = take(4 * E), o_x1 = take(4 * E), o_gx = take(4 * E), o_gy = take(4 * E),
+                     o_gsel = take(4 * NU * (size_t)c.n_layers), o_gw = take(4 * NU * (size_t)c.n_layers);
+        OPEN_CK(dalloc((void **)&h->gs_base, o), "scratch");
+        unsigned char *b = h->gs_base;
+        h->gs.logits = (float *)(b + o_lg); h->gs.hd = (float *)(b + o_hd); h->gs.dn = (float *)(b + o_dn); h->gs.h = (float *)(b + o_h); h->gs.acc = (float *)(b + o_acc);
+        h->gs.in_q = (signed char *)(b + o_q); h->gs.in_s = (float *)(b + o_s); h->gs.in_c = (int *)(b + o_c);
+        h->gs.sel_asc = (int *)(b + o_sel); h->gs.cw = (float *)(b + o_cw); h->gs.status = h->status;
+        h->gs.xbuf[0] = (float *)(b + o_x0); h->gs.xbuf[1] = (float *)(b + o_x1);
+        h->gs.prev_post_ffw1 = h->gs.prev_post_ffw2 = h->gs.prev_post_ffw = nullptr;
+        h->g_x = (float *)(b + o_gx); h->g_y = (float *)(b + o_gy); h->g_sel = (int32_t *)(b + o_gsel); h->g_wts = (float *)(b + o_gw);
+        const char *ev = getenv("SP_MOE_DECODE_IMPL");          /* house convention: behaviour switches are SP_* variables read once */
+        h->decode_impl = (ev && ev[0] == 'p') ? 1 : 0;
+        cudaDeviceGetAttribute(&h->sms, cudaDevAttrMultiProcessorCount, c.device);
+    }
     { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
     OPEN_CK(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     h->last_stream = h->stream;
@@ -171,7 +197,8 @@ extern "C" int sp_moe_close(sp_moe *h) {
     cudaSetDevice(h->device);
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
     sp_batched_free(&h->bs);
-    void *ps[] = {h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
+    for (auto &g : h->graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
+    void *ps[] = {h->gs_base, h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
     for (void *p : ps) if (p) cudaFree(p);
     cudaGetLastError();
     delete h;
@@ -228,6 +255,34 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream;
     h->last_stream = st;
+    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE && h->decode_impl == 0) {
+        const bool routing = sel_dev || wts_dev;
+        sp_moe::DecodeGraph *dg = nullptr;
+        for (auto &g : h->graphs) if (g.lf == lf && g.nl == nl && g.routing == routing) dg = &g;
+        if (!dg) {                                                   /* first use: capture the layer run once */
+            cudaStream_t cs = h->stream;
+            cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr; int nlaunch = 0;
+            CK(cudaStreamSynchronize(cs), "stream synchronize");
+            CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal), "begin capture");
+            cudaError_t e = sp_graph_decode_enqueue(h->d, h->layers_host.data(), lf, nl, h->g_x, h->g_y, routing ? h->g_sel : nullptr,
+                                                    routing ? h->g_wts : nullptr, h->gs, h->sms, cs, true, &nlaunch);
+            cudaError_t e2 = cudaStreamEndCapture(cs, &graph);
+            if (e != cudaSuccess || e2 != cudaSuccess) { if (graph) cudaGraphDestroy(graph); cudaGetLastError(); return fail_cuda(e != cudaSuccess ? e : e2, "decode graph capture"); }
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return fail_cuda(e, "decode graph instantiate");
+            h->graphs.push_back({lf, nl, routing, exec, nlaunch});
+            dg = &h->graphs.back();
+        }
+        const size_t nb = (size_t)h->cfg.E * 4, ns = (size_t)nl * h->cfg.NU * 4;
+        CK(cudaMemcpyAsync(h->g_x, x_dev, nb, cudaMemcpyDeviceToDevice, st), "x staging");
+        CK(cudaGraphLaunch(dg->exec, st), "decode graph launch");
+        CK(cudaMemcpyAsync(y_dev, h->g_y, nb, cudaMemcpyDeviceToDevice, st), "y staging");
+        if (sel_dev) CK(cudaMemcpyAsync(sel_dev, h->g_sel, ns, cudaMemcpyDeviceToDevice, st), "sel staging");
+        if (wts_dev) CK(cudaMemcpyAsync(wts_dev, h->g_wts, ns, cudaMemcpyDeviceToDevice, st), "wts staging");
+        h->launches += (uint64_t)dg->launches;
+        return SP_MOE_OK;
+    }
     if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
         /* at most 64 layers per launch (the bias mask is one word): longer runs chain launches */
         const float *xin = x_dev;

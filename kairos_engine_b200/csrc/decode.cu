@@ -58,7 +58,7 @@ constexpr int kThreads = kCons + 32;       /* + one producer warp = 16 warps: 4 
 constexpr int kSlot = 16384;               /* ring slot bytes */
 constexpr int kMaxSlots = 12;
 constexpr unsigned kSpinLimit = 1u << 22;  /* polls before a wait gives up (order of a second) */
-constexpr int kMaxInFlight = 4;            /* chunks the producer keeps in flight: enough for full HBM rate (measured), while a
+constexpr int kMaxInFlight = 8;            /* chunks the producer keeps in flight: enough for full HBM rate (measured), while a
                                               deeper queue only delays the small exchange loads that share the memory system */
 constexpr unsigned kPollNs = 128;          /* pause between polls of another CTA's word: polling must not flood L2 */
 

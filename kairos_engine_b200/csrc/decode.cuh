@@ -29,3 +29,16 @@ int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_b
 int sp_decode_threads();
 cudaError_t sp_decode_prepare(const SpDims &d, size_t smem, int *max_grid);
 cudaError_t sp_decode_launch(const SpDecodeArgs &args, int grid, size_t smem, cudaStream_t st);
+
+/* ---- the three-kernels-per-layer decode path (decode_graph.cu) ---- */
+struct SpGraphScratch {
+    float *logits, *hd, *dn, *h, *acc;          /* [NE] [FFS] [E] [NU*FFE] [E] */
+    signed char *in_q; float *in_s; int *in_c;  /* the routed experts' quantised input, [E] / [E/16] */
+    int *sel_asc; float *cw;                    /* [NU] */
+    int *status;
+    float *xbuf[2];                             /* residual between layers, ping-pong */
+    const float *prev_post_ffw1, *prev_post_ffw2, *prev_post_ffw;   /* set per launch */
+};
+size_t sp_graph_scratch_bytes(const SpDims &d);
+cudaError_t sp_graph_decode_enqueue(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl, const float *x_in, float *y_out,
+                                    int32_t *sel, float *wts, const SpGraphScratch &sc, int sms, cudaStream_t st, bool pdl, int *nlaunch);
