@@ -131,6 +131,20 @@ int sp_moe_q4b_dequantize_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, 
 int sp_moe_gemv_q4b_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int in, int rows,
                         const float *x_dev, float *y_dev, void *stream);
 
+/* sp_moe_gemv_q4b_dev without any allocation. NO COUNTERPART IN THE REFERENCE (there the caller of
+ * gemv_w_packed owns the int8 scratch). For callers that must not allocate device memory when they
+ * call - a serving loop that has committed the whole card to pre-sized arenas, where cudaMalloc can
+ * fail and where cudaMalloc / cudaFree stall every stream of the device, or a component that only
+ * ever works in buffers its host hands it. The int8 scratch is a fixed array inside the library
+ * (6 KB per device that loads it, held until exit), so `in` is limited to 4096; larger values are
+ * refused with SP_MOE_EBADARG. The call enqueues on `stream` and returns; it calls no cudaMalloc,
+ * cudaFree or other allocating routine. The FIRST call on each device also looks up the array's
+ * device address (cudaGetSymbolAddress): make that first call before opening any stream capture.
+ * Every call shares the one array and leaves its last contents there: two calls whose kernels can
+ * overlap on the GPU (different streams) race on it - keep them on one stream or order them. */
+int sp_moe_gemv_q4b_static_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int in, int rows,
+                               const float *x_dev, float *y_dev, void *stream);
+
 /* k_gelu_mul (CF:1364-1373): out[i] = gelu_tanh(g[i]) * up[i] on DEVICE memory, in the library's
  * bit-reproducible arithmetic (the tanh is a fixed sequence of correctly-rounded operations). */
 int sp_moe_gelu_mul_dev(const float *g_dev, const float *up_dev, int64_t n, float *out_dev, void *stream);

@@ -15,6 +15,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <vector>
 
 namespace {
@@ -182,5 +183,58 @@ extern "C" int sp_moe_gemv_q4b_dev(const uint8_t *codes_dev, const uint16_t *bs_
     cudaFree(q); cudaFree(sx); cudaFree(corr);
     if (e != cudaSuccess) { char b[256]; snprintf(b, sizeof b, "sp_moe_gemv_q4b_dev: %s", cudaGetErrorString(e)); sp_set_error(b); cudaGetLastError();
         return e == cudaErrorMemoryAllocation ? SP_MOE_EBACKEND_OOM : SP_MOE_ECUDA; }
+    return SP_MOE_OK;
+}
+
+/* ---------------------------------------------------------------- the same GEMV with no allocation
+ * Some callers must not allocate device memory when they call: a serving loop that has already
+ * committed the whole card to pre-sized arenas (cudaMalloc can then fail, and cudaMalloc/cudaFree
+ * stall every stream of the device while they run), or a component that is handed buffers by its
+ * host and has no business touching the allocator at all. For them the int8 scratch of the GEMV
+ * lives in this fixed array, which every device that loads the library holds until the process
+ * exits: SP_MOE_GEMV_STATIC_MAX_IN codes + two 4-byte words per 16 inputs = 6 KB.
+ *
+ * In host code the array's name is only a stand-in; the device address comes from
+ * cudaGetSymbolAddress, asked once per device with that device current. */
+#define SP_MOE_GEMV_STATIC_MAX_IN 4096
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[SP_MOE_GEMV_STATIC_MAX_IN + 2 * 4 * (SP_MOE_GEMV_STATIC_MAX_IN / 16)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char *g_static_ptr[kMaxDevices];     /* device address of the array, per device; NULL until set up */
+}
+
+extern "C" int sp_moe_gemv_q4b_static_dev(const uint8_t *codes_dev, const uint16_t *bs_dev, int in, int rows,
+                                          const float *x_dev, float *y_dev, void *stream) {
+    if (!codes_dev || !bs_dev || !x_dev || !y_dev || in <= 0 || rows <= 0 || (in & 31)) {
+        sp_set_error("sp_moe_gemv_q4b_static_dev: bad argument (in must be a positive multiple of 32)"); return SP_MOE_EBADARG; }
+    if (in > SP_MOE_GEMV_STATIC_MAX_IN) {
+        char b[192]; snprintf(b, sizeof b, "sp_moe_gemv_q4b_static_dev: in=%d exceeds the fixed scratch (at most %d inputs); use sp_moe_gemv_q4b_dev", in, SP_MOE_GEMV_STATIC_MAX_IN);
+        sp_set_error(b); return SP_MOE_EBADARG; }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess && (dev < 0 || dev >= kMaxDevices)) { sp_set_error("sp_moe_gemv_q4b_static_dev: device ordinal out of range"); return SP_MOE_EUNSUPPORTED; }
+    unsigned char *base = nullptr;
+    if (e == cudaSuccess) {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_ptr[dev]) {                                 /* first call on this device: look the array up */
+            void *p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_gemv_static_scratch);
+            if (e == cudaSuccess) g_static_ptr[dev] = static_cast<unsigned char *>(p);
+        }
+        base = g_static_ptr[dev];
+    }
+    if (e == cudaSuccess) {
+        cudaStream_t st = (cudaStream_t)stream;
+        signed char *q = reinterpret_cast<signed char *>(base);
+        float *sx = reinterpret_cast<float *>(base + SP_MOE_GEMV_STATIC_MAX_IN);
+        int *corr = reinterpret_cast<int *>(base + SP_MOE_GEMV_STATIC_MAX_IN + 4 * (SP_MOE_GEMV_STATIC_MAX_IN / 16));
+        /* nothing in the scratch has to start at zero: the quantiser writes every byte the GEMV reads */
+        k_sa_quant<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
+        k_sa_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) { char b[256]; snprintf(b, sizeof b, "sp_moe_gemv_q4b_static_dev: %s", cudaGetErrorString(e)); sp_set_error(b); cudaGetLastError(); return SP_MOE_ECUDA; }
     return SP_MOE_OK;
 }
