@@ -30,9 +30,10 @@ CFG = dict(E=2816, NE=128, NU=8, FFE=704, FFS=2112, eps=1e-6)
 N_LAYERS = 30
 TOKENS_PER_STEP = 256
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu
-# capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers),
+# from the ncu capture summarised in profiles/decode_graph_m1.md: per layer 8.30 + 25.82 + 8.97 MB
+# read and 0.07 MB written
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 30 * (8299520 + 25816064 + 8971520 + 70000)
 
 
 def measured_peak():
@@ -158,14 +159,15 @@ def run_ours(args, rank, local_rank, world):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    eng = MoeEngine(n_layers=N_LAYERS, max_tokens=1, device=local_rank, **CFG)
-    for L in range(N_LAYERS):
+    NL = args.layers
+    eng = MoeEngine(n_layers=NL, max_tokens=1, device=local_rank, **CFG)
+    for L in range(NL):
         layer = synth.make_layer(CFG, 1000 * L, device=f"cuda:{local_rank}")
         eng.upload_layer(L, layer, on_device=True)
         del layer
     torch.cuda.empty_cache()
     E = CFG["E"]
-    T = TOKENS_PER_STEP
+    T = args.tokens_per_step
     xs = synth.make_inputs(CFG, T, seed=7 + rank, device=f"cuda:{local_rank}")      # resident inputs
     ys = torch.empty_like(xs)
     stream = torch.cuda.current_stream()
@@ -221,17 +223,17 @@ def run_ours(args, rank, local_rank, world):
 
     if rank == 0:
         peak, peak_kind = measured_peak()
-        bytes_per_launch = N_LAYERS * synth.algorithmic_bytes_per_layer(CFG, M=1, U=CFG["NU"])
+        bytes_per_launch = NL * synth.algorithmic_bytes_per_layer(CFG, M=1, U=CFG["NU"])
         launch_ms = ms / (T * args.steps)                 # one launch = one token through 30 layers
         achieved = bytes_per_launch / (launch_ms / 1e3) / 1e9
         line = {"metric": "MoE-FFN decode tokens/s (30-layer stack, M=1)", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "int8 activations x int4 weights, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "configs[1]: 30-layer MoE FFN stack (Gemma-4-26B-A4B geometry), decode M=1, 256 sequential tokens per step, "
-                                       "all experts resident", "layers": N_LAYERS, "tokens_per_step": T, "parallelism": "replicas" if world > 1 else "single GPU",
+                                       "all experts resident", "layers": NL, "tokens_per_step": T, "parallelism": "replicas" if world > 1 else "single GPU",
                            "l2": "weights 13.2 GB per pass, far larger than L2: no flush needed"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": bytes_per_launch, "kernel": "k_moe_decode_stack",
+                             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if NL == N_LAYERS else None, "algorithmic_bytes_per_launch": bytes_per_launch, "kernel": "decode graph: per layer k_dg_router_shared + k_dg_experts_up + k_dg_experts_down (one graph launch = one token through the stack)",
                              "launch_ms": launch_ms},
                 "e2e": {"value": e2e_v, "unit": "tokens/s", "h2d_bytes_per_step": T * E * 4, "d2h_bytes_per_step": T * E * 4},
                 "gpu_launches": int(launches), "clocks": clk.summary()}
@@ -240,7 +242,7 @@ def run_ours(args, rank, local_rank, world):
                 threads = min(os.cpu_count() or 1, 16)
                 layers = cpu_layers(3, torch)
                 cpu_time_tokens(layers, 1, threads)
-                n_tok = 8
+                n_tok = 192
                 secs, kind = cpu_time_tokens(layers, n_tok, threads, seed=1)
                 line["cpu_baseline"] = {"value": n_tok / secs, "unit": "tokens/s", "cores": threads, "kind": kind,
                                         "sample": f"{n_tok} tokens x 30 layers, layer pool of 3 cycled (cold weights), {secs:.1f} s"}
@@ -259,6 +261,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP, help="profiling aid: fewer sequential tokens per step than the workload's 256")
+    ap.add_argument("--layers", type=int, default=N_LAYERS, help="profiling aid: a shorter stack than the workload's 30 layers (not a bench result)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
