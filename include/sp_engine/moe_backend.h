@@ -104,6 +104,28 @@ int  sp_moe_forward_dev(sp_moe *h, int layer_first, int n_layers, int flavour, i
 /* Synchronises the handle's last stream and returns 0 or the error a kernel recorded. */
 int  sp_moe_status(sp_moe *h);
 
+/* One layer of g4_ffn_apply cut where (token, expert) pairs would change GPU, for expert-parallel
+ * prefill (the reference is single-GPU: its expert-major loop, CF:8925-8965, visits every expert
+ * on the one device; here each GPU owns a contiguous block of experts and the caller moves rows
+ * between the stages with an all-to-all). DEVICE pointers, enqueue only, one layer in flight per
+ * handle (the shared-expert branch and the combine weights wait in the handle between route and
+ * finish).
+ *   route   : x[M][E] -> sel_asc[M][NU] (each token's experts, ascending id), cw[M][NU] (combine
+ *             weight = renormalised probability * down-scale, same order), rows[M][E] (the routed
+ *             experts' input: x normalised with pre_ffw_norm_2); sel/wts as in sp_moe_forward (or NULL)
+ *   experts : rows_in[n_rows][E] sorted by expert, expert e owning rows [offsets[e], offsets[e+1])
+ *             (offsets: NE+1 ints, device memory) -> rows_out[n_rows][E] = down(geglu(gate|up(row)));
+ *             n_rows <= max_tokens * NU
+ *   finish  : pair_rows[M][NU][E] in sel_asc order -> y = the layer's output residual
+ * A run through the three stages is bit-identical to sp_moe_forward_dev on the same tokens. */
+int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,
+                        int32_t *sel_asc_dev, float *cw_dev, float *rows_dev,
+                        int32_t *sel_dev, float *wts_dev, void *stream);
+int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev,
+                          const int32_t *offsets_dev, float *rows_out_dev, void *stream);
+int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev,
+                         float *y_dev, void *stream);
+
 /* The reference's standalone single-token operator, verbatim signature (CF:13821-13825).
  * All pointers are HOST memory; allocates, uploads the whole expert set, runs, frees.
  * Its semantics differ from the layer above (one weightless norm, no shared expert, no

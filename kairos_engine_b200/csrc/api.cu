@@ -318,6 +318,56 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
     return SP_MOE_OK;
 }
 
+/* ---------------------------------------------------------------- expert-parallel stages (one layer) */
+static int check_ep(sp_moe *h, int L, int flavour, const char *who) {
+    if (!h) return fail(SP_MOE_EBADARG, "%s: NULL handle", who);
+    if (L < 0 || L >= h->cfg.n_layers) return fail(SP_MOE_EBADARG, "%s: layer %d out of range [0, %d)", who, L, h->cfg.n_layers);
+    if (flavour != SP_MOE_FLAVOUR_DECODE && flavour != SP_MOE_FLAVOUR_PREFILL) return fail(SP_MOE_EBADARG, "%s: unknown flavour %d", who, flavour);
+    if (!h->uploaded[L]) return fail(SP_MOE_EBADSTATE, "%s: layer %d has no weights uploaded", who, L);
+    return SP_MOE_OK;
+}
+extern "C" int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev, int32_t *sel_asc_dev, float *cw_dev,
+                                   float *rows_dev, int32_t *sel_dev, float *wts_dev, void *stream) {
+    int rc = check_ep(h, layer, flavour, "sp_moe_ep_route_dev");
+    if (rc) return rc;
+    if (!x_dev || !sel_asc_dev || !cw_dev || !rows_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: NULL argument");
+    if (M <= 0 || M > h->cfg.max_tokens) return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: M=%d outside (0, max_tokens=%d]", M, h->cfg.max_tokens);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_ep_route(h->d, h->layers_host[layer], flavour, M, x_dev, sel_asc_dev, cw_dev, rows_dev, sel_dev, wts_dev,
+                                        &h->bs, h->status, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel route launch");
+}
+extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev, const int32_t *offsets_dev,
+                                     float *rows_out_dev, void *stream) {
+    int rc = check_ep(h, layer, flavour, "sp_moe_ep_experts_dev");
+    if (rc) return rc;
+    if (n_rows < 0 || (long long)n_rows > (long long)h->cfg.max_tokens * h->cfg.NU)
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_experts_dev: n_rows=%d outside [0, max_tokens*NU=%lld]", n_rows, (long long)h->cfg.max_tokens * h->cfg.NU);
+    if (n_rows == 0) return SP_MOE_OK;
+    if (!rows_in_dev || !offsets_dev || !rows_out_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_experts_dev: NULL argument");
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_ep_experts(h->d, h->layers_host[layer], flavour, n_rows, rows_in_dev, offsets_dev, rows_out_dev, &h->bs, h->status, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel expert launch");
+}
+extern "C" int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev, float *y_dev, void *stream) {
+    int rc = check_ep(h, layer, SP_MOE_FLAVOUR_DECODE, "sp_moe_ep_finish_dev");
+    if (rc) return rc;
+    if (!x_dev || !pair_rows_dev || !y_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_finish_dev: NULL argument");
+    if (M <= 0 || M > h->cfg.max_tokens) return fail(SP_MOE_EBADARG, "sp_moe_ep_finish_dev: M=%d outside (0, max_tokens=%d]", M, h->cfg.max_tokens);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_ep_finish(h->d, h->layers_host[layer], M, x_dev, pair_rows_dev, y_dev, &h->bs, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel finish launch");
+}
+
 extern "C" int sp_moe_status(sp_moe *h) {
     if (!h) return fail(SP_MOE_EBADARG, "sp_moe_status: NULL handle");
     CK(cudaSetDevice(h->device), "cudaSetDevice");

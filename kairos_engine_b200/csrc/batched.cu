@@ -15,6 +15,8 @@
  * experts in ascending id with acc = acc + w*out, so results do not depend on scheduling.
  */
 #include "batched.cuh"
+#include "prefill_tc.cuh"
+#include <cstdlib>
 #include "../../include/sp_engine/moe_backend.h"
 
 namespace {
@@ -24,7 +26,8 @@ struct BView {                 /* carved scratch */
     signed char *nx_q, *in_q, *hd_q, *h_q;
     float *nx_s, *in_s, *hd_s, *h_s;
     int *nx_c, *in_c, *hd_c, *h_c;
-    int *sel_asc, *count, *list;
+    int *sel_asc, *count, *list, *pairpos;
+    signed char *ep_q; float *ep_s; int *ep_c;      /* expert-parallel stage: quantised received rows, [max_tokens*NU] rows */
 };
 
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -41,10 +44,12 @@ size_t blayout(const SpDims &d, int Mx, F place) {
     take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* s */
     take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* c */
     take(4 * M * NU); take(4 * NE); take(4 * NE * M);                                               /* sel_asc count list */
+    take(M * NU * E); take(4 * M * NU * (E / 16)); take(4 * M * NU * (E / 16));                     /* ep_q ep_s ep_c */
+    take(4 * M * NU);                                                                               /* pairpos */
     return o;
 }
 BView bview(const SpDims &d, const SpBatchedScratch *s) {
-    unsigned char *p[26];
+    unsigned char *p[30];
     blayout(d, s->max_tokens, [&](int id, size_t off) { p[id] = (unsigned char *)s->base + off; });
     BView v;
     v.rin = (float *)p[0]; v.nx_f = (float *)p[1]; v.in_f = (float *)p[2]; v.logits = (float *)p[3]; v.cw = (float *)p[4];
@@ -53,6 +58,7 @@ BView bview(const SpDims &d, const SpBatchedScratch *s) {
     v.nx_s = (float *)p[15]; v.in_s = (float *)p[16]; v.hd_s = (float *)p[17]; v.h_s = (float *)p[18];
     v.nx_c = (int *)p[19]; v.in_c = (int *)p[20]; v.hd_c = (int *)p[21]; v.h_c = (int *)p[22];
     v.sel_asc = (int *)p[23]; v.count = (int *)p[24]; v.list = (int *)p[25];
+    v.ep_q = (signed char *)p[26]; v.ep_s = (float *)p[27]; v.ep_c = (int *)p[28]; v.pairpos = (int *)p[29];
     return v;
 }
 
@@ -99,7 +105,7 @@ __device__ __forceinline__ void quant_row(int n, signed char *q, float *sx, int 
 
 /* ---------------------------------------------------------------- K1: per-token norms of x (CF:8347, 8402-8404, 8425) */
 template <bool FA>
-__global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const float *x, BView v) {
+__global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const float *x, BView v, float *rows_f) {
     __shared__ double sh[256];
     const int t = blockIdx.x, E = d.E;
     const float *xt = x + (size_t)t * E;
@@ -109,11 +115,15 @@ __global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const fl
         const size_t b16 = (size_t)t * (E / 16);
         quant_row(E, v.nx_q + (size_t)t * E, v.nx_s + b16, v.nx_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.ffn_norm + i)); });
         quant_row(E, v.in_q + (size_t)t * E, v.in_s + b16, v.in_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i)); });
+        if (rows_f)                                             /* the routed experts' input as fp32 rows (expert-parallel dispatch) */
+            for (int i = threadIdx.x; i < E; i += 256) rows_f[(size_t)t * E + i] = __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i));
     } else {
         for (int i = threadIdx.x; i < E; i += 256) {
             const float xs = __fmul_rn(xt[i], scale);
             v.nx_f[(size_t)t * E + i] = __fmul_rn(xs, __ldg(L.ffn_norm + i));
-            v.in_f[(size_t)t * E + i] = __fmul_rn(xs, __ldg(L.pre_ffw2 + i));
+            const float iv = __fmul_rn(xs, __ldg(L.pre_ffw2 + i));
+            v.in_f[(size_t)t * E + i] = iv;
+            if (rows_f) rows_f[(size_t)t * E + i] = iv;
         }
     }
     for (int i = threadIdx.x; i < E; i += 256)
@@ -202,6 +212,7 @@ __global__ void __launch_bounds__(256) k_b_topk(SpDims d, SpLayerDev L, BView v,
         v.sel_asc[pair] = e;
         v.cw[pair] = __fmul_rn(w, __ldg(L.dexps_scale + e));             /* CF:8709 */
         const int pos = atomicAdd(&v.count[e], 1);
+        v.pairpos[pair] = pos;
         if (pos < M) v.list[(size_t)e * M + pos] = pair; else atomicExch(status, SP_KERR_OVERFLOW);
         if (sel_out) sel_out[(size_t)tok * NU + t] = e;
         if (wts_out) wts_out[(size_t)tok * NU + t] = w;
@@ -224,6 +235,7 @@ struct GroupArgs {
     const uint8_t *codes; const uint16_t *bs;      /* tensor base */
     long long rows_per_group;                      /* row stride between groups */
     const int *count, *list; int list_stride;      /* per-group lists (NULL list = identity 0..M-1) */
+    const int *offset;                             /* or: group g owns items [offset[g], offset[g+1]) (rows sorted by expert) */
     int M, in, rows;                               /* rows (or pairs) per group */
     int up_off;                                    /* PAIR: row offset of the up row */
     const uint8_t *ucodes; const uint16_t *ubs;    /* PAIR with a separate up tensor (shared expert), else NULL */
@@ -295,8 +307,9 @@ template <bool FA, bool PAIR, int NIT>
 __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
-    const int cnt = g.count ? g.count[grp] : g.M;
-    if (cnt == 0) return;
+    const int first = g.offset ? g.offset[grp] : 0;
+    const int cnt = g.offset ? g.offset[grp + 1] - first : (g.count ? g.count[grp] : g.M);
+    if (cnt <= 0) return;
     const int r = blockIdx.x * 8 + warp;
     if (r >= g.rows) return;
     const int n32 = g.in >> 5;
@@ -311,7 +324,7 @@ __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     const int *list = g.list ? g.list + (size_t)grp * g.list_stride : nullptr;
     const int b16 = g.in >> 4;
     for (int i = 0; i < cnt; i++) {
-        const int item = list ? list[i] : i;
+        const int item = list ? list[i] : first + i;
         const size_t arow = (size_t)(item / g.act_div);
         float o;
         if (FA) {
@@ -340,7 +353,7 @@ void launch_rows(const GroupArgs &g, int groups, cudaStream_t st, int *nl) {
 }
 
 /* ---------------------------------------------------------------- K7: ordered combine + recombine (CF:6071-6077, 9014-9019) */
-__global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, float *y) {
+__global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, const float *eo, float *y) {
     extern __shared__ __align__(16) float fsm[];              /* [2][E] */
     __shared__ double sh[256];
     const int t = blockIdx.x, E = d.E, NU = d.NU;
@@ -351,7 +364,7 @@ __global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const 
     for (int i = threadIdx.x; i < E; i += 256) {
         float acc = 0.0f;
 #pragma unroll
-        for (int k = 0; k < SP_MAX_NU; k++) if (k < NU) acc = __fadd_rn(acc, __fmul_rn(cw[k], v.eo[((size_t)t * NU + k) * E + i]));
+        for (int k = 0; k < SP_MAX_NU; k++) if (k < NU) acc = __fadd_rn(acc, __fmul_rn(cw[k], eo[((size_t)t * NU + k) * E + i]));
         vb[i] = acc;
         va[i] = v.dn[(size_t)t * E + i];
     }
@@ -371,9 +384,9 @@ __global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const 
 
 template <bool FA>
 cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *x, float *y, int32_t *sel, float *wts,
-                      BView &v, int *status, cudaStream_t st, int *nl) {
+                      BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
-    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v); (*nl)++;
+    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, nullptr); (*nl)++;
     {
         const size_t sm = (size_t)8 * E * 4;
         cudaError_t e = cudaFuncSetAttribute(k_b_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
@@ -381,6 +394,17 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
         k_b_router<<<dim3((NE + 7) / 8, (M + kRouterTT - 1) / kRouterTT), 256, sm, st>>>(d, L, v, M); (*nl)++;
     }
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
+    if (!FA && tc) {                                            /* prefill arithmetic on the tensor cores */
+        cudaError_t e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
+        if (e != cudaSuccess) return e;
+        const int *off, *gather, *rowmap;
+        e = sp_tc_sort_pairs(tc, d, M, v.sel_asc, v.count, v.pairpos, &off, &gather, &rowmap, st, nl);
+        if (e != cudaSuccess) return e;
+        e = sp_tc_routed(tc, d, L, M * NU, v.in_f, gather, off, rowmap, v.eo, status, st, nl);
+        if (e != cudaSuccess) return e;
+        k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, y); (*nl)++;
+        return cudaGetLastError();
+    }
     GroupArgs g{};
     g.M = M;
     /* shared expert gate/up -> hd (CF:8348-8356) */
@@ -403,20 +427,120 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
     g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E; g.count = v.count; g.list = v.list; g.list_stride = M;
     g.in = FFE; g.rows = E; g.act_div = 1; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = v.eo; g.out_stride = E;
     launch_rows<FA, false>(g, NE, st, nl);
-    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, y); (*nl)++;
+    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, y); (*nl)++;
+    return cudaGetLastError();
+}
+
+/* ---------------------------------------------------------------- expert-parallel stages
+ * The layer cut at the two places where (token, expert) pairs change GPU:
+ *   route   : norms, router, top-k, the shared expert (kept in this handle's scratch), and the
+ *             routed experts' input rows;
+ *   experts : gate|up GeGLU + down for rows that arrive sorted by expert, on whichever GPU owns
+ *             those experts (any subset: empty groups cost nothing);
+ *   finish  : ordered combine of the returned pair rows + the recombine.
+ * The arithmetic of each pair is the single-GPU batched path's, so a split run is bit-identical. */
+template <bool FA>
+cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows,
+                     int32_t *sel, float *wts, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+    const int E = d.E, NE = d.NE, NU = d.NU, FFS = d.FFS;
+    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, rows); (*nl)++;
+    const size_t sm = (size_t)8 * E * 4;
+    cudaError_t e = cudaFuncSetAttribute(k_b_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return e;
+    k_b_router<<<dim3((NE + 7) / 8, (M + kRouterTT - 1) / kRouterTT), 256, sm, st>>>(d, L, v, M); (*nl)++;
+    k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
+    if (!FA && tc) {
+        e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
+        if (e != cudaSuccess) return e;
+        e = cudaMemcpyAsync(sel_asc, v.sel_asc, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return e;
+        return cudaMemcpyAsync(cw, v.cw, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
+    }
+    GroupArgs g{};
+    g.M = M;
+    g.codes = L.sg_codes; g.bs = L.sg_bs; g.ucodes = L.su_codes; g.ubs = L.su_bs;
+    g.in = E; g.rows = FFS; g.act_div = 1; g.q = v.nx_q; g.sx = v.nx_s; g.corr = v.nx_c; g.xf = v.nx_f; g.out = v.hd; g.out_stride = FFS;
+    launch_rows<FA, true>(g, 1, st, nl);
+    if (FA) { k_b_quant_rows<<<M, 256, 0, st>>>(v.hd, FFS, v.hd_q, v.hd_s, v.hd_c); (*nl)++; }
+    g.codes = L.sd_codes; g.bs = L.sd_bs; g.ucodes = nullptr; g.ubs = nullptr;
+    g.in = FFS; g.rows = E; g.q = v.hd_q; g.sx = v.hd_s; g.corr = v.hd_c; g.xf = v.hd; g.out = v.dn; g.out_stride = E;
+    launch_rows<FA, false>(g, 1, st, nl);
+    e = cudaMemcpyAsync(sel_asc, v.sel_asc, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyAsync(cw, v.cw, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return e;
+    return cudaGetLastError();
+}
+
+template <bool FA>
+cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float *rows_in, const int32_t *offsets, float *rows_out,
+                       BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+    const int E = d.E, NE = d.NE, FFE = d.FFE;
+    if (R == 0) return cudaSuccess;
+    if (!FA && tc) return sp_tc_routed(tc, d, L, R, rows_in, nullptr, offsets, nullptr, rows_out, status, st, nl);
+    if (FA) { k_b_quant_rows<<<R, 256, 0, st>>>(rows_in, E, v.ep_q, v.ep_s, v.ep_c); (*nl)++; }
+    GroupArgs g{};
+    g.M = R; g.offset = offsets;
+    g.codes = L.gu_codes; g.bs = L.gu_bs; g.rows_per_group = 2LL * FFE;
+    g.in = E; g.rows = FFE; g.up_off = FFE; g.act_div = 1; g.q = v.ep_q; g.sx = v.ep_s; g.corr = v.ep_c; g.xf = rows_in; g.out = v.h; g.out_stride = FFE;
+    launch_rows<FA, true>(g, NE, st, nl);
+    if (FA) { k_b_quant_rows<<<R, 256, 0, st>>>(v.h, FFE, v.h_q, v.h_s, v.h_c); (*nl)++; }
+    g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E;
+    g.in = FFE; g.rows = E; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = rows_out; g.out_stride = E;
+    launch_rows<FA, false>(g, NE, st, nl);
     return cudaGetLastError();
 }
 
 }  // namespace
 
+cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
+                                float *rows, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+    *nlaunch = 0;
+    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
+    BView v = bview(d, s);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch)
+                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch);
+}
+cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *offsets,
+                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+    *nlaunch = 0;
+    if (!s->base || (long long)R > (long long)s->max_tokens * d.NU) return cudaErrorInvalidValue;
+    BView v = bview(d, s);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch)
+                                            : ep_experts<false>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch);
+}
+cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, float *y,
+                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch) {
+    *nlaunch = 0;
+    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
+    BView v = bview(d, s);
+    k_b_finish<<<M, 256, (size_t)2 * d.E * 4, st>>>(d, L, x, v, pair_rows, y); (*nlaunch)++;
+    return cudaGetLastError();
+}
+
 cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *s, size_t *bytes) {
     s->base = nullptr; s->bytes = 0; s->max_tokens = max_tokens; *bytes = 0;
     s->bytes = blayout(d, max_tokens, [](int, size_t) {});
-    const cudaError_t e = cudaMalloc(&s->base, s->bytes);
-    if (e == cudaSuccess) *bytes = s->bytes; else s->base = nullptr;
-    return e;
+    s->tc = nullptr;
+    cudaError_t e = cudaMalloc(&s->base, s->bytes);
+    if (e != cudaSuccess) { s->base = nullptr; return e; }
+    *bytes = s->bytes;
+    /* house convention: behaviour switches are SP_* variables read once. "simt" keeps prefill on the fp32 CUDA-core kernels. */
+    const char *ev = getenv("SP_MOE_PREFILL_IMPL");
+    if (max_tokens > 1 && sp_tc_supported(d) && !(ev && ev[0] == 's')) {
+        size_t tb = 0;
+        e = sp_tc_create(d, max_tokens, &s->tc, &tb);
+        if (e != cudaSuccess) { cudaFree(s->base); s->base = nullptr; return e; }
+        *bytes += tb;
+    }
+    return cudaSuccess;
 }
-void sp_batched_free(SpBatchedScratch *s) { if (s && s->base) cudaFree(s->base); if (s) s->base = nullptr; }
+void sp_batched_free(SpBatchedScratch *s) {
+    if (!s) return;
+    if (s->tc) { sp_tc_destroy(s->tc); s->tc = nullptr; }
+    if (s->base) cudaFree(s->base);
+    s->base = nullptr;
+}
 
 cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl_, int flavour, int M,
                                const float *x, float *y, int32_t *sel, float *wts,
@@ -430,8 +554,8 @@ cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, i
         int32_t *sl = sel ? sel + (size_t)li * M * d.NU : nullptr;
         float *wl = wts ? wts + (size_t)li * M * d.NU : nullptr;
         const cudaError_t e = (flavour == SP_MOE_FLAVOUR_DECODE)
-            ? run_layer<true>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, status, st, nlaunch)
-            : run_layer<false>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, status, st, nlaunch);
+            ? run_layer<true>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, s->tc, status, st, nlaunch)
+            : run_layer<false>(d, layers_host[lf + li], M, cur, dst, sl, wl, v, s->tc, status, st, nlaunch);
         if (e != cudaSuccess) return e;
         cur = dst;
     }

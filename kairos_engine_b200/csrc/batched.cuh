@@ -7,6 +7,7 @@ struct SpBatchedScratch {
     void *base;            /* one allocation carved into the buffers the kernels use */
     size_t bytes;
     int max_tokens;
+    struct SpTcPlan *tc;   /* tensor-core prefill plan, NULL when the geometry or the switch rules it out */
 };
 
 cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *s, size_t *bytes);
@@ -16,3 +17,16 @@ void sp_batched_free(SpBatchedScratch *s);
 cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl, int flavour, int M,
                                const float *x, float *y, int32_t *sel, float *wts,
                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+
+/* The same layer cut into the three stages an expert-parallel run needs (one layer at a time;
+ * the shared-expert result and the combine weights stay in the scratch between route and finish).
+ *   route   : sel_asc[M*NU] (expert ids per token, ascending), cw[M*NU] (combine weights in that
+ *             order), rows[M*E] (the routed experts' input rows)
+ *   experts : R rows sorted by expert, group e = rows [offsets[e], offsets[e+1]); R <= max_tokens*NU
+ *   finish  : pair_rows[(t*NU+k)*E] = output of token t's k-th expert in ascending id order */
+cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
+                                float *rows, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *offsets,
+                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, float *y,
+                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch);

@@ -100,6 +100,36 @@ class MoeEngine:
     def status(self):
         check(_lib.lib().sp_moe_status(self._h))
 
+    # -- one layer in three stages (expert-parallel runs move rows between them; see ep.py)
+    def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None):
+        """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 [M][E])."""
+        import torch
+        M, NU = x.shape[0], self.cfg["NU"]
+        sel_asc = torch.empty((M, NU), dtype=torch.int32, device=x.device)
+        cw = torch.empty((M, NU), dtype=torch.float32, device=x.device)
+        rows = torch.empty_like(x)
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        check(_lib.lib().sp_moe_ep_route_dev(self._h, layer, flavour, M, x.data_ptr(), sel_asc.data_ptr(), cw.data_ptr(),
+                                             rows.data_ptr(), _ptr(sel), _ptr(wts), st))
+        return sel_asc, cw, rows
+
+    def ep_experts(self, layer, rows, offsets, flavour=FLAVOUR_PREFILL):
+        """rows torch CUDA f32 [R][E] sorted by expert, offsets int32 [NE+1] -> the experts' outputs [R][E]."""
+        import torch
+        out = torch.empty_like(rows)
+        st = torch.cuda.current_stream(rows.device).cuda_stream
+        check(_lib.lib().sp_moe_ep_experts_dev(self._h, layer, flavour, rows.shape[0], rows.data_ptr(), offsets.data_ptr(),
+                                               out.data_ptr(), st))
+        return out
+
+    def ep_finish(self, layer, x, pair_rows):
+        """x [M][E], pair_rows [M][NU][E] (each token's expert outputs, ascending expert id) -> y [M][E]."""
+        import torch
+        y = torch.empty_like(x)
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        check(_lib.lib().sp_moe_ep_finish_dev(self._h, layer, x.shape[0], x.data_ptr(), pair_rows.data_ptr(), y.data_ptr(), st))
+        return y
+
 
 def q4b_quantize(w):
     """torch CUDA f32 [rows][cols] -> (codes uint8 [rows][cols/2], scales int16-view f16 [rows][cols/32])."""
