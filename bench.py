@@ -149,6 +149,60 @@ def run_reference(args, rank, world):
         dist.barrier(); dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------- prefill (reported beside the decode metric)
+def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
+    """PT tokens through the stack in the prefill arithmetic: one GPU runs them all; N GPUs run
+    PT/N tokens each with the routed experts partitioned NE/N per GPU (all-to-all each way)."""
+    import torch
+    from kairos_engine_b200 import FLAVOUR_PREFILL, ep, synth
+    Ml = PT // world
+    xp = synth.make_inputs(CFG, Ml, seed=99 + rank, device=f"cuda:{local_rank}")
+    yp = torch.empty_like(xp)
+    epm = ep.ExpertParallelMoe(eng, CFG) if world > 1 else None
+
+    def one_pass():
+        if epm is None:
+            eng.forward_dev(xp, yp, 0, NL, FLAVOUR_PREFILL)
+        else:
+            epm.forward(xp, 0, NL, FLAVOUR_PREFILL)
+
+    for _ in range(2):
+        one_pass()
+    eng.status()
+    barrier()
+    passes = 3
+    l0 = eng.kernel_launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(passes):
+        one_pass()
+    e1.record()
+    barrier()
+    eng.status()
+    ms = e0.elapsed_time(e1)
+    rows = float(epm.last_rows) if epm is not None else float(Ml * CFG["NU"])
+    if dist is not None:
+        t = torch.tensor([ms, rows, -rows], device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, rows_max, rows_min = float(t[0]), float(t[1]), -float(t[2])
+    else:
+        rows_max = rows_min = rows
+    flops = synth.flops_per_token_layer(CFG) * PT * NL * passes
+    tf = flops / (ms / 1e3) / 1e12 / world
+    peak_tf = None
+    try:
+        peak_tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+    except Exception:
+        pass
+    return {"metric": "MoE-FFN prefill tokens/s (30-layer stack)", "value": PT * passes / (ms / 1e3), "unit": "tokens/s", "tokens": PT,
+            "ms_per_pass": ms / passes, "passes": passes, "dtype": "f16 x f16 split operands (3 MMAs per k-step), f32 accumulate in TMEM",
+            "parallelism": "single GPU" if world == 1 else f"expert-parallel: {PT // world} tokens and {CFG['NE'] // world} experts per GPU, all-to-all each way",
+            "expert_rows_last_layer": {"max_per_gpu": rows_max, "min_per_gpu": rows_min},
+            "gpu_launches": int(eng.kernel_launches - l0),
+            "tensor": {"algorithmic_tflops_per_gpu": tf, "peak": peak_tf, "frac": (tf / peak_tf) if peak_tf else None,
+                       "note": "algorithmic FLOPs (2*M*N*K once) over the whole pass, all kernels included; the MMAs issued are 3x that"}}
+
+
 # ---------------------------------------------------------------- our arm
 def run_ours(args, rank, local_rank, world):
     import numpy as np
@@ -160,7 +214,8 @@ def run_ours(args, rank, local_rank, world):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     NL = args.layers
-    eng = MoeEngine(n_layers=NL, max_tokens=1, device=local_rank, **CFG)
+    PT = 0 if args.no_prefill else max(world, args.prefill_tokens // world * world)      # prefill tokens of the whole job
+    eng = MoeEngine(n_layers=NL, max_tokens=max(1, PT // world), device=local_rank, **CFG)
     for L in range(NL):
         layer = synth.make_layer(CFG, 1000 * L, device=f"cuda:{local_rank}")
         eng.upload_layer(L, layer, on_device=True)
@@ -221,6 +276,8 @@ def run_ours(args, rank, local_rank, world):
         e2e_s = float(ts.item())
     e2e_v = T * e2e_steps * world / e2e_s
 
+    prefill = prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier) if PT else None
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         bytes_per_launch = NL * synth.algorithmic_bytes_per_layer(CFG, M=1, U=CFG["NU"])
@@ -229,7 +286,7 @@ def run_ours(args, rank, local_rank, world):
         line = {"metric": "MoE-FFN decode tokens/s (30-layer stack, M=1)", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "int8 activations x int4 weights, f32 accumulate", "data": "synthetic",
-                "config": {"workload": "configs[1]: 30-layer MoE FFN stack (Gemma-4-26B-A4B geometry), decode M=1, 256 sequential tokens per step, "
+                "config": {"workload": "configs[1]: 30-layer MoE FFN stack (Gemma-4-26B-A4B geometry), decode M=1, sequential tokens, "
                                        "all experts resident", "layers": NL, "tokens_per_step": T, "parallelism": "replicas" if world > 1 else "single GPU",
                            "l2": "weights 13.2 GB per pass, far larger than L2: no flush needed"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
@@ -237,6 +294,8 @@ def run_ours(args, rank, local_rank, world):
                              "launch_ms": launch_ms},
                 "e2e": {"value": e2e_v, "unit": "tokens/s", "h2d_bytes_per_step": T * E * 4, "d2h_bytes_per_step": T * E * 4},
                 "gpu_launches": int(launches), "clocks": clk.summary()}
+        if prefill:
+            line["prefill"] = prefill
         if world == 1 and not args.no_cpu:
             try:
                 threads = min(os.cpu_count() or 1, 16)
@@ -262,6 +321,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP, help="profiling aid: fewer sequential tokens per step than the workload's 256")
+    ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill leg (whole job)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="profiling aid: a shorter stack than the workload's 30 layers (not a bench result)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

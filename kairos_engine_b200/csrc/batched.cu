@@ -133,33 +133,58 @@ __global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const fl
 /* ---------------------------------------------------------------- K2: router logits, fp32, fixed order
  * lane l takes the float4 groups q = l, l+32, ... with acc = fma(w, x, acc) over the four
  * elements in order, then the shuffle tree (the same order the decode kernel uses). One block =
- * 8 experts (one per warp) x TT tokens; the 8 router rows sit in shared memory. */
-constexpr int kRouterTT = 16;
+ * 16 experts x 16 tokens; E is walked in chunks of 64 float4 groups staged in shared memory, and
+ * each warp keeps a 4-expert x 8-token register tile, so every (expert, token) chain keeps the
+ * order above while 32 independent chains hide the FMA latency. */
+constexpr int kRouterTE = 16, kRouterTT = 16;
 __global__ void __launch_bounds__(256) k_b_router(SpDims d, SpLayerDev L, BView v, int M) {
-    extern __shared__ __align__(16) float wsm[];              /* [8][E] */
-    const int E = d.E, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x * 8 + warp, t0 = blockIdx.y * kRouterTT;
-    for (int i = threadIdx.x; i < 8 * (E >> 2); i += 256) {
-        const int r = i / (E >> 2), q = i - r * (E >> 2);
-        const int er = blockIdx.x * 8 + r;
-        reinterpret_cast<float4 *>(wsm)[i] = er < d.NE ? __ldg(reinterpret_cast<const float4 *>(L.router_w + (size_t)er * E) + q) : make_float4(0, 0, 0, 0);
-    }
-    __syncthreads();
-    if (e >= d.NE) return;
-    const float *wrow = wsm + (size_t)warp * E;
-    const float bias = L.router_bias ? __ldg(L.router_bias + e) : 0.0f;
-    for (int t = t0; t < t0 + kRouterTT && t < M; t++) {
-        const float *rin = v.rin + (size_t)t * E;
-        float acc = 0.0f;
-        for (int q = lane; q < (E >> 2); q += 32) {
-            const float4 w = *reinterpret_cast<const float4 *>(wrow + 4 * q);
-            const float4 xv = __ldg(reinterpret_cast<const float4 *>(rin) + q);
-            acc = __fmaf_rn(w.x, xv.x, acc); acc = __fmaf_rn(w.y, xv.y, acc);
-            acc = __fmaf_rn(w.z, xv.z, acc); acc = __fmaf_rn(w.w, xv.w, acc);
+    __shared__ float4 wS[kRouterTE][64];
+    __shared__ float4 xS[kRouterTT][64];
+    const int E = d.E, G = E >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int we = warp & 3, wt = warp >> 2;
+    const int e0 = blockIdx.x * kRouterTE, t0 = blockIdx.y * kRouterTT;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+    const float4 zero = make_float4(0, 0, 0, 0);
+    for (int c0 = 0; c0 < G; c0 += 64) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 16 * 64; idx += 256) {
+            const int row = idx >> 6, g = idx & 63, gg = c0 + g;
+            wS[row][g] = (gg < G && e0 + row < d.NE) ? __ldg(reinterpret_cast<const float4 *>(L.router_w + (size_t)(e0 + row) * E) + gg) : zero;
+            xS[row][g] = (gg < G && t0 + row < M) ? *(reinterpret_cast<const float4 *>(v.rin + (size_t)(t0 + row) * E) + gg) : zero;
         }
-        acc = warp_tree(acc);
-        if (lane == 0) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(acc, bias) : acc;
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int g = lane + 32 * h;            /* zero padding beyond E leaves acc unchanged: fma(0, 0, acc) = acc */
+            float4 w[4], x[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++) w[i] = wS[4 * we + i][g];
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = xS[8 * wt + j][g];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float a = acc[i][j];
+                    a = __fmaf_rn(w[i].x, x[j].x, a); a = __fmaf_rn(w[i].y, x[j].y, a);
+                    a = __fmaf_rn(w[i].z, x[j].z, a); a = __fmaf_rn(w[i].w, x[j].w, a);
+                    acc[i][j] = a;
+                }
+        }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float r = warp_tree(acc[i][j]);
+            const int e = e0 + 4 * we + i, t = t0 + 8 * wt + j;
+            if (lane == 0 && e < d.NE && t < M)
+                v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, __ldg(L.router_bias + e)) : r;
+        }
 }
 
 /* ---------------------------------------------------------------- K3: moe_topk_host (CF:6220-6240) + bucketing by expert (CF:8594-8624) */
@@ -361,6 +386,7 @@ __global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const 
     float cw[SP_MAX_NU];
 #pragma unroll
     for (int k = 0; k < SP_MAX_NU; k++) cw[k] = k < NU ? v.cw[(size_t)t * NU + k] : 0.0f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < E; i += 256) {
         float acc = 0.0f;
 #pragma unroll
@@ -388,10 +414,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
     const int E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
     k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, nullptr); (*nl)++;
     {
-        const size_t sm = (size_t)8 * E * 4;
-        cudaError_t e = cudaFuncSetAttribute(k_b_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-        if (e != cudaSuccess) return e;
-        k_b_router<<<dim3((NE + 7) / 8, (M + kRouterTT - 1) / kRouterTT), 256, sm, st>>>(d, L, v, M); (*nl)++;
+        k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
     }
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
     if (!FA && tc) {                                            /* prefill arithmetic on the tensor cores */
@@ -444,10 +467,8 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
                      int32_t *sel, float *wts, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, NU = d.NU, FFS = d.FFS;
     k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, rows); (*nl)++;
-    const size_t sm = (size_t)8 * E * 4;
-    cudaError_t e = cudaFuncSetAttribute(k_b_router, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    if (e != cudaSuccess) return e;
-    k_b_router<<<dim3((NE + 7) / 8, (M + kRouterTT - 1) / kRouterTT), 256, sm, st>>>(d, L, v, M); (*nl)++;
+    cudaError_t e = cudaSuccess;
+    k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
     if (!FA && tc) {
         e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);

@@ -43,3 +43,14 @@ def assert_close(y, ref, what=""):
     rel = np.linalg.norm(d) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30)
     assert max_abs <= MAX_ABS and rel <= REL_L2, f"{what}: max-abs {max_abs:.3e} (<= {MAX_ABS}), rel-L2 {rel:.3e} (<= {REL_L2})"
     return max_abs, rel
+
+
+def assert_same_experts(sel, rsel, wts, rwts, margin, tie=1e-6):
+    """Prefill arithmetic (floating-point GEMMs whose summation order differs from the checker's):
+    every token must pick the same SET of experts; the descending-probability order inside the
+    set may differ from the checker's only between experts whose weights tie within `tie`."""
+    assert np.array_equal(np.sort(sel, axis=-1), np.sort(rsel, axis=-1)), f"expert sets differ (min top-8/9 margin {margin:.3e})"
+    swapped = sel != rsel
+    if swapped.any():
+        assert np.abs(np.sort(wts, axis=-1) - np.sort(rwts, axis=-1))[swapped.any(axis=-1)].max() <= tie
+        assert np.abs(wts - rwts)[swapped].max() <= tie, "order inside the selection differs beyond a tie"

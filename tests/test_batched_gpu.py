@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import orc
-from gpu_common import assert_close, make_stack, oracle_stack
+from gpu_common import assert_close, assert_same_experts, make_stack, oracle_stack
 
 pytestmark = pytest.mark.gpu
 A, B = 0, 1
@@ -32,8 +32,8 @@ def test_batched_prefill_flavour_small(cfg, n_layers, M):
     x = np.random.default_rng(M + 100).standard_normal((M, cfg["E"])).astype(np.float32)
     y, sel, wts = eng.forward(x, flavour=B)
     ry, rsel, rwts, margin = oracle_stack(cfg, host, x, B)
-    assert np.array_equal(sel, rsel), f"expert ids differ (min margin {margin:.3e})"
-    np.testing.assert_allclose(wts, rwts, rtol=1e-6, atol=1e-7)
+    assert_same_experts(sel, rsel, wts, rwts, margin)
+    np.testing.assert_allclose(np.sort(wts, axis=-1), np.sort(rwts, axis=-1), rtol=1e-5, atol=1e-7)
     assert_close(y, ry, "batched prefill flavour")
     eng.close()
 
