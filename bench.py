@@ -215,7 +215,7 @@ def run_ours(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     NL = args.layers
     PT = 0 if args.no_prefill else max(world, args.prefill_tokens // world * world)      # prefill tokens of the whole job
-    eng = MoeEngine(n_layers=NL, max_tokens=max(1, PT // world), device=local_rank, **CFG)
+    eng = MoeEngine(n_layers=NL, max_tokens=max(1, PT // world), device=local_rank, max_expert_rows=PT * CFG["NU"] if world > 1 else 0, **CFG)
     for L in range(NL):
         layer = synth.make_layer(CFG, 1000 * L, device=f"cuda:{local_rank}")
         eng.upload_layer(L, layer, on_device=True)

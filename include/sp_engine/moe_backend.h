@@ -56,7 +56,9 @@ typedef struct {
     int32_t max_tokens;  /* largest M a forward call may pass */
     int32_t device;      /* CUDA device ordinal */
     float   eps;
-    int32_t reserved[7]; /* zero */
+    int32_t max_expert_rows; /* rows one sp_moe_ep_experts_dev call may pass; 0 = max_tokens * NU. An
+                                expert-parallel rank can receive up to (tokens of the whole job) * NU */
+    int32_t reserved[6]; /* zero */
 } sp_moe_config;
 
 /* One layer's weights in the reference's layouts (sp_model.h:50-53, CF:1448-1464, 6179-6193):
@@ -115,7 +117,7 @@ int  sp_moe_status(sp_moe *h);
  *             experts' input: x normalised with pre_ffw_norm_2); sel/wts as in sp_moe_forward (or NULL)
  *   experts : rows_in[n_rows][E] sorted by expert, expert e owning rows [offsets[e], offsets[e+1])
  *             (offsets: NE+1 ints, device memory) -> rows_out[n_rows][E] = down(geglu(gate|up(row)));
- *             n_rows <= max_tokens * NU
+ *             n_rows <= max_expert_rows of the config
  *   finish  : pair_rows[M][NU][E] in sel_asc order -> y = the layer's output residual
  * A run through the three stages is bit-identical to sp_moe_forward_dev on the same tokens. */
 int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,

@@ -19,7 +19,8 @@ EXPORTS = ("sp_last_error", "sp_set_error", "sp_moe_open", "sp_moe_close", "sp_m
 class SpMoeConfig(C.Structure):
     _fields_ = [("E", C.c_int32), ("NE", C.c_int32), ("NU", C.c_int32), ("FFE", C.c_int32),
                 ("FFS", C.c_int32), ("n_layers", C.c_int32), ("max_tokens", C.c_int32),
-                ("device", C.c_int32), ("eps", C.c_float), ("reserved", C.c_int32 * 7)]
+                ("device", C.c_int32), ("eps", C.c_float), ("max_expert_rows", C.c_int32),
+                ("reserved", C.c_int32 * 6)]
 
 
 _PTR_FIELDS = ("router_w", "router_scale", "router_bias", "ffn_norm", "post_ffw1", "pre_ffw2",

@@ -119,6 +119,7 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     if (c.NE <= 0 || c.NE > 1024 || c.NU <= 0 || c.NU > SP_MAX_NU || c.NU > c.NE)
         return fail(SP_MOE_EBADARG, "sp_moe_open: need 0 < NU <= min(NE, %d), NE <= 1024 (got NE=%d NU=%d)", SP_MAX_NU, c.NE, c.NU);
     if (c.n_layers <= 0 || c.max_tokens <= 0) return fail(SP_MOE_EBADARG, "sp_moe_open: n_layers and max_tokens must be positive");
+    if (c.max_expert_rows < 0) return fail(SP_MOE_EBADARG, "sp_moe_open: max_expert_rows must not be negative");
     int ndev = 0;
     cudaError_t e = cudaGetDeviceCount(&ndev);
     if (e != cudaSuccess || ndev == 0) { cudaGetLastError(); return fail(SP_MOE_ECUDA, "sp_moe_open: no CUDA device (%s); this library has no CPU path", cudaGetErrorString(e)); }
@@ -171,7 +172,7 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         h->decode_impl = (ev && ev[0] == 'p') ? 1 : 0;
         cudaDeviceGetAttribute(&h->sms, cudaDevAttrMultiProcessorCount, c.device);
     }
-    { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
+    { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, c.max_expert_rows, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
     OPEN_CK(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     h->last_stream = h->stream;
     h->scratch_bytes = sb;
@@ -344,8 +345,9 @@ extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_ro
                                      float *rows_out_dev, void *stream) {
     int rc = check_ep(h, layer, flavour, "sp_moe_ep_experts_dev");
     if (rc) return rc;
-    if (n_rows < 0 || (long long)n_rows > (long long)h->cfg.max_tokens * h->cfg.NU)
-        return fail(SP_MOE_EBADARG, "sp_moe_ep_experts_dev: n_rows=%d outside [0, max_tokens*NU=%lld]", n_rows, (long long)h->cfg.max_tokens * h->cfg.NU);
+    if (n_rows < 0 || n_rows > h->bs.max_rows)
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_experts_dev: n_rows=%d outside [0, max_expert_rows=%d] (set sp_moe_config.max_expert_rows for the "
+                                    "worst case an expert-parallel rank can receive)", n_rows, h->bs.max_rows);
     if (n_rows == 0) return SP_MOE_OK;
     if (!rows_in_dev || !offsets_dev || !rows_out_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_experts_dev: NULL argument");
     CK(cudaSetDevice(h->device), "cudaSetDevice");

@@ -27,30 +27,30 @@ struct BView {                 /* carved scratch */
     float *nx_s, *in_s, *hd_s, *h_s;
     int *nx_c, *in_c, *hd_c, *h_c;
     int *sel_asc, *count, *list, *pairpos;
-    signed char *ep_q; float *ep_s; int *ep_c;      /* expert-parallel stage: quantised received rows, [max_tokens*NU] rows */
+    signed char *ep_q; float *ep_s; int *ep_c;      /* expert-parallel stage: quantised received rows, [max_rows] */
 };
 
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <class F>
-size_t blayout(const SpDims &d, int Mx, F place) {
+size_t blayout(const SpDims &d, int Mx, int Rx, F place) {
     size_t o = 0; int id = 0;
     auto take = [&](size_t bytes) { place(id++, o); o = up256(o + bytes); };
-    const size_t M = Mx, E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
+    const size_t M = Mx, R = Rx, E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;    /* R >= M * NU */
     take(4 * M * E); take(4 * M * E); take(4 * M * E); take(4 * M * NE); take(4 * M * NU);            /* rin nx_f in_f logits cw */
-    take(4 * M * FFS); take(4 * M * E); take(4 * M * NU * FFE); take(4 * M * NU * E);                /* hd dn h eo */
+    take(4 * M * FFS); take(4 * M * E); take(4 * R * FFE); take(4 * M * NU * E);                     /* hd dn h eo */
     take(4 * M * E); take(4 * M * E);                                                               /* xa xb */
-    take(M * E); take(M * E); take(M * FFS); take(M * NU * FFE);                                     /* q */
-    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* s */
-    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * M * NU * (FFE / 16));   /* c */
+    take(M * E); take(M * E); take(M * FFS); take(R * FFE);                                          /* q */
+    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * R * (FFE / 16));        /* s */
+    take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * R * (FFE / 16));        /* c */
     take(4 * M * NU); take(4 * NE); take(4 * NE * M);                                               /* sel_asc count list */
-    take(M * NU * E); take(4 * M * NU * (E / 16)); take(4 * M * NU * (E / 16));                     /* ep_q ep_s ep_c */
+    take(R * E); take(4 * R * (E / 16)); take(4 * R * (E / 16));                                    /* ep_q ep_s ep_c */
     take(4 * M * NU);                                                                               /* pairpos */
     return o;
 }
 BView bview(const SpDims &d, const SpBatchedScratch *s) {
     unsigned char *p[30];
-    blayout(d, s->max_tokens, [&](int id, size_t off) { p[id] = (unsigned char *)s->base + off; });
+    blayout(d, s->max_tokens, s->max_rows, [&](int id, size_t off) { p[id] = (unsigned char *)s->base + off; });
     BView v;
     v.rin = (float *)p[0]; v.nx_f = (float *)p[1]; v.in_f = (float *)p[2]; v.logits = (float *)p[3]; v.cw = (float *)p[4];
     v.hd = (float *)p[5]; v.dn = (float *)p[6]; v.h = (float *)p[7]; v.eo = (float *)p[8]; v.xa = (float *)p[9]; v.xb = (float *)p[10];
@@ -525,7 +525,7 @@ cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavou
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
-    if (!s->base || (long long)R > (long long)s->max_tokens * d.NU) return cudaErrorInvalidValue;
+    if (!s->base || R > s->max_rows) return cudaErrorInvalidValue;
     BView v = bview(d, s);
     return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch)
                                             : ep_experts<false>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch);
@@ -539,9 +539,10 @@ cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, co
     return cudaGetLastError();
 }
 
-cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *s, size_t *bytes) {
+cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, int max_rows, SpBatchedScratch *s, size_t *bytes) {
     s->base = nullptr; s->bytes = 0; s->max_tokens = max_tokens; *bytes = 0;
-    s->bytes = blayout(d, max_tokens, [](int, size_t) {});
+    s->max_rows = max_rows > max_tokens * d.NU ? max_rows : max_tokens * d.NU;
+    s->bytes = blayout(d, max_tokens, s->max_rows, [](int, size_t) {});
     s->tc = nullptr;
     cudaError_t e = cudaMalloc(&s->base, s->bytes);
     if (e != cudaSuccess) { s->base = nullptr; return e; }
@@ -550,7 +551,7 @@ cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *
     const char *ev = getenv("SP_MOE_PREFILL_IMPL");
     if (max_tokens > 1 && sp_tc_supported(d) && !(ev && ev[0] == 's')) {
         size_t tb = 0;
-        e = sp_tc_create(d, max_tokens, &s->tc, &tb);
+        e = sp_tc_create(d, max_tokens, s->max_rows, &s->tc, &tb);
         if (e != cudaSuccess) { cudaFree(s->base); s->base = nullptr; return e; }
         *bytes += tb;
     }

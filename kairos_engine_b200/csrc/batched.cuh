@@ -7,10 +7,11 @@ struct SpBatchedScratch {
     void *base;            /* one allocation carved into the buffers the kernels use */
     size_t bytes;
     int max_tokens;
+    int max_rows;          /* rows the expert stage accepts (>= max_tokens * NU) */
     struct SpTcPlan *tc;   /* tensor-core prefill plan, NULL when the geometry or the switch rules it out */
 };
 
-cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, SpBatchedScratch *s, size_t *bytes);
+cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, int max_rows, SpBatchedScratch *s, size_t *bytes);
 void sp_batched_free(SpBatchedScratch *s);
 /* Runs layers [lf, lf+nl) on M tokens; enqueues only. *nlaunch = kernels launched.
  * layers_host: HOST array of the layers' device views (they ride as kernel parameters). */

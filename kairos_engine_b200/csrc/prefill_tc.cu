@@ -388,7 +388,7 @@ cudaError_t make_map(EncodeTiledFn fn, CUtensorMap *m, void *ptr, int K, int row
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 }  // namespace
 
-cudaError_t sp_tc_create(const SpDims &d, int max_tokens, SpTcPlan **out, size_t *bytes) {
+cudaError_t sp_tc_create(const SpDims &d, int max_tokens, int max_rows, SpTcPlan **out, size_t *bytes) {
     *out = nullptr; *bytes = 0;
     if (!sp_tc_supported(d)) return cudaSuccess;
     void *fnp = nullptr; cudaDriverEntryPointQueryResult qres;
@@ -397,7 +397,7 @@ cudaError_t sp_tc_create(const SpDims &d, int max_tokens, SpTcPlan **out, size_t
     if (!fnp || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
     SpTcPlan *p = new SpTcPlan();
     p->Mcap = ((max_tokens + kTileN - 1) / kTileN) * kTileN;
-    p->Rcap = (int)((((long long)max_tokens * d.NU + kTileN - 1) / kTileN) * kTileN);
+    p->Rcap = (int)((((long long)max_rows + kTileN - 1) / kTileN) * kTileN);
     int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&p->sms, cudaDevAttrMultiProcessorCount, dev);
     p->cap_sh = p->Mcap / kTileN + 2; p->cap_r = p->Rcap / kTileN + d.NE + 2;
     size_t o = 0; auto take = [&](size_t b) { size_t at = o; o = up256(o + b); return at; };

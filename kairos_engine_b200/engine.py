@@ -34,11 +34,11 @@ def _ptr(a):
 class MoeEngine:
     """Owns one sp_moe handle: the resident arena of every layer's experts plus scratch."""
 
-    def __init__(self, E, NE, NU, FFE, FFS, n_layers, max_tokens=1, eps=1e-6, device=0):
+    def __init__(self, E, NE, NU, FFE, FFS, n_layers, max_tokens=1, eps=1e-6, device=0, max_expert_rows=0):
         self.cfg = dict(E=E, NE=NE, NU=NU, FFE=FFE, FFS=FFS, eps=eps)
         self.n_layers, self.max_tokens, self.device = n_layers, max_tokens, device
         c = SpMoeConfig(E=E, NE=NE, NU=NU, FFE=FFE, FFS=FFS, n_layers=n_layers,
-                        max_tokens=max_tokens, device=device, eps=eps)
+                        max_tokens=max_tokens, device=device, eps=eps, max_expert_rows=max_expert_rows)
         self._h = C.c_void_p()
         check(_lib.lib().sp_moe_open(C.byref(c), C.byref(self._h)))
 
