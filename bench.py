@@ -30,10 +30,9 @@ CFG = dict(E=2816, NE=128, NU=8, FFE=704, FFS=2112, eps=1e-6)
 N_LAYERS = 30
 TOKENS_PER_STEP = 256
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers),
-# from the ncu capture summarised in profiles/decode_graph_m1.md: per layer 8.30 + 25.82 + 8.97 MB
-# read and 0.07 MB written
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 30 * (8299520 + 25816064 + 8971520 + 70000)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers), from the ncu
+# launch list summarised in profiles/decode_graph_m1.md (caches kept between kernels, as in a real run)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1164866112
 
 
 def measured_peak():
