@@ -115,18 +115,22 @@ int  sp_moe_status(sp_moe *h);
  *   route   : x[M][E] -> sel_asc[M][NU] (each token's experts, ascending id), cw[M][NU] (combine
  *             weight = renormalised probability * down-scale, same order), rows[M][E] (the routed
  *             experts' input: x normalised with pre_ffw_norm_2); sel/wts as in sp_moe_forward (or NULL)
- *   experts : rows_in[n_rows][E] sorted by expert, expert e owning rows [offsets[e], offsets[e+1])
- *             (offsets: NE+1 ints, device memory) -> rows_out[n_rows][E] = down(geglu(gate|up(row)));
+ *   experts : rows_in[n_rows][E] -> rows_out[n_rows][E] = down(geglu(gate|up(row))) with the weights of
+ *             the row's expert. Sorted by expert, position p belongs to expert e when
+ *             offsets[e] <= p < offsets[e+1] (offsets: NE+1 ints, device memory) and is row
+ *             row_index[p] of rows_in / rows_out; row_index NULL = the rows are already sorted.
  *             n_rows <= max_expert_rows of the config
- *   finish  : pair_rows[M][NU][E] in sel_asc order -> y = the layer's output residual
+ *   finish  : token t's k-th expert output (sel_asc order) is row pair_index[t*NU+k] of pair_rows
+ *             (pair_index NULL = row t*NU+k) -> y = the layer's output residual
  * A run through the three stages is bit-identical to sp_moe_forward_dev on the same tokens. */
 int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,
                         int32_t *sel_asc_dev, float *cw_dev, float *rows_dev,
                         int32_t *sel_dev, float *wts_dev, void *stream);
 int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev,
-                          const int32_t *offsets_dev, float *rows_out_dev, void *stream);
+                          const int32_t *row_index_dev, const int32_t *offsets_dev, float *rows_out_dev,
+                          void *stream);
 int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev,
-                         float *y_dev, void *stream);
+                         const int32_t *pair_index_dev, float *y_dev, void *stream);
 
 /* The reference's standalone single-token operator, verbatim signature (CF:13821-13825).
  * All pointers are HOST memory; allocates, uploads the whole expert set, runs, frees.

@@ -341,8 +341,8 @@ extern "C" int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, con
     h->launches += (uint64_t)nlaunch;
     return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel route launch");
 }
-extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev, const int32_t *offsets_dev,
-                                     float *rows_out_dev, void *stream) {
+extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev, const int32_t *row_index_dev,
+                                     const int32_t *offsets_dev, float *rows_out_dev, void *stream) {
     int rc = check_ep(h, layer, flavour, "sp_moe_ep_experts_dev");
     if (rc) return rc;
     if (n_rows < 0 || n_rows > h->bs.max_rows)
@@ -353,11 +353,12 @@ extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_ro
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
     int nlaunch = 0;
-    cudaError_t e = sp_batched_ep_experts(h->d, h->layers_host[layer], flavour, n_rows, rows_in_dev, offsets_dev, rows_out_dev, &h->bs, h->status, st, &nlaunch);
+    cudaError_t e = sp_batched_ep_experts(h->d, h->layers_host[layer], flavour, n_rows, rows_in_dev, row_index_dev, offsets_dev, rows_out_dev, &h->bs, h->status, st, &nlaunch);
     h->launches += (uint64_t)nlaunch;
     return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel expert launch");
 }
-extern "C" int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev, float *y_dev, void *stream) {
+extern "C" int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev, const int32_t *pair_index_dev,
+                                    float *y_dev, void *stream) {
     int rc = check_ep(h, layer, SP_MOE_FLAVOUR_DECODE, "sp_moe_ep_finish_dev");
     if (rc) return rc;
     if (!x_dev || !pair_rows_dev || !y_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_finish_dev: NULL argument");
@@ -365,7 +366,7 @@ extern "C" int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
     int nlaunch = 0;
-    cudaError_t e = sp_batched_ep_finish(h->d, h->layers_host[layer], M, x_dev, pair_rows_dev, y_dev, &h->bs, st, &nlaunch);
+    cudaError_t e = sp_batched_ep_finish(h->d, h->layers_host[layer], M, x_dev, pair_rows_dev, pair_index_dev, y_dev, &h->bs, st, &nlaunch);
     h->launches += (uint64_t)nlaunch;
     return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel finish launch");
 }

@@ -261,6 +261,7 @@ struct GroupArgs {
     long long rows_per_group;                      /* row stride between groups */
     const int *count, *list; int list_stride;      /* per-group lists (NULL list = identity 0..M-1) */
     const int *offset;                             /* or: group g owns items [offset[g], offset[g+1]) (rows sorted by expert) */
+    const int *index;                              /* with offset: sorted position -> row in the buffers (NULL = identity) */
     int M, in, rows;                               /* rows (or pairs) per group */
     int up_off;                                    /* PAIR: row offset of the up row */
     const uint8_t *ucodes; const uint16_t *ubs;    /* PAIR with a separate up tensor (shared expert), else NULL */
@@ -349,7 +350,7 @@ __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     const int *list = g.list ? g.list + (size_t)grp * g.list_stride : nullptr;
     const int b16 = g.in >> 4;
     for (int i = 0; i < cnt; i++) {
-        const int item = list ? list[i] : first + i;
+        const int item = list ? list[i] : (g.index ? g.index[first + i] : first + i);
         const size_t arow = (size_t)(item / g.act_div);
         float o;
         if (FA) {
@@ -378,19 +379,22 @@ void launch_rows(const GroupArgs &g, int groups, cudaStream_t st, int *nl) {
 }
 
 /* ---------------------------------------------------------------- K7: ordered combine + recombine (CF:6071-6077, 9014-9019) */
-__global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, const float *eo, float *y) {
+__global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, const float *eo, const int *pair_index, float *y) {
     extern __shared__ __align__(16) float fsm[];              /* [2][E] */
     __shared__ double sh[256];
     const int t = blockIdx.x, E = d.E, NU = d.NU;
     float *va = fsm, *vb = fsm + E;
-    float cw[SP_MAX_NU];
+    float cw[SP_MAX_NU]; size_t er[SP_MAX_NU];
 #pragma unroll
-    for (int k = 0; k < SP_MAX_NU; k++) cw[k] = k < NU ? v.cw[(size_t)t * NU + k] : 0.0f;
+    for (int k = 0; k < SP_MAX_NU; k++) {
+        cw[k] = k < NU ? v.cw[(size_t)t * NU + k] : 0.0f;
+        er[k] = k < NU ? (size_t)(pair_index ? pair_index[(size_t)t * NU + k] : t * NU + k) * E : 0;
+    }
 #pragma unroll 4
     for (int i = threadIdx.x; i < E; i += 256) {
         float acc = 0.0f;
 #pragma unroll
-        for (int k = 0; k < SP_MAX_NU; k++) if (k < NU) acc = __fadd_rn(acc, __fmul_rn(cw[k], eo[((size_t)t * NU + k) * E + i]));
+        for (int k = 0; k < SP_MAX_NU; k++) if (k < NU) acc = __fadd_rn(acc, __fmul_rn(cw[k], eo[er[k] + i]));
         vb[i] = acc;
         va[i] = v.dn[(size_t)t * E + i];
     }
@@ -425,7 +429,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
         if (e != cudaSuccess) return e;
         e = sp_tc_routed(tc, d, L, M * NU, v.in_f, gather, off, rowmap, v.eo, status, st, nl);
         if (e != cudaSuccess) return e;
-        k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, y); (*nl)++;
+        k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
         return cudaGetLastError();
     }
     GroupArgs g{};
@@ -450,7 +454,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
     g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E; g.count = v.count; g.list = v.list; g.list_stride = M;
     g.in = FFE; g.rows = E; g.act_div = 1; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = v.eo; g.out_stride = E;
     launch_rows<FA, false>(g, NE, st, nl);
-    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, y); (*nl)++;
+    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
     return cudaGetLastError();
 }
 
@@ -494,14 +498,14 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
 }
 
 template <bool FA>
-cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float *rows_in, const int32_t *offsets, float *rows_out,
+cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets, float *rows_out,
                        BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, FFE = d.FFE;
     if (R == 0) return cudaSuccess;
-    if (!FA && tc) return sp_tc_routed(tc, d, L, R, rows_in, nullptr, offsets, nullptr, rows_out, status, st, nl);
+    if (!FA && tc) return sp_tc_routed(tc, d, L, R, rows_in, row_index, offsets, row_index, rows_out, status, st, nl);
     if (FA) { k_b_quant_rows<<<R, 256, 0, st>>>(rows_in, E, v.ep_q, v.ep_s, v.ep_c); (*nl)++; }
     GroupArgs g{};
-    g.M = R; g.offset = offsets;
+    g.M = R; g.offset = offsets; g.index = row_index;
     g.codes = L.gu_codes; g.bs = L.gu_bs; g.rows_per_group = 2LL * FFE;
     g.in = E; g.rows = FFE; g.up_off = FFE; g.act_div = 1; g.q = v.ep_q; g.sx = v.ep_s; g.corr = v.ep_c; g.xf = rows_in; g.out = v.h; g.out_stride = FFE;
     launch_rows<FA, true>(g, NE, st, nl);
@@ -522,20 +526,20 @@ cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavou
     return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch)
                                             : ep_route<false>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch);
 }
-cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *offsets,
+cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
     if (!s->base || R > s->max_rows) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch)
-                                            : ep_experts<false>(d, L, R, rows_in, offsets, rows_out, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, row_index, offsets, rows_out, v, s->tc, status, st, nlaunch)
+                                            : ep_experts<false>(d, L, R, rows_in, row_index, offsets, rows_out, v, s->tc, status, st, nlaunch);
 }
-cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, float *y,
+cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,
                                  SpBatchedScratch *s, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
     if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    k_b_finish<<<M, 256, (size_t)2 * d.E * 4, st>>>(d, L, x, v, pair_rows, y); (*nlaunch)++;
+    k_b_finish<<<M, 256, (size_t)2 * d.E * 4, st>>>(d, L, x, v, pair_rows, pair_index, y); (*nlaunch)++;
     return cudaGetLastError();
 }
 

@@ -11,6 +11,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import SpMoeConfig, SpMoeLayerWeights, check
+from .trace import RouteTrace
 
 FLAVOUR_DECODE = 0     # int8 activation quant + exact integer dots (reference decode arithmetic)
 FLAVOUR_PREFILL = 1    # exact Q4B dequant + floating-point GEMM (reference prefill arithmetic)
@@ -41,6 +42,7 @@ class MoeEngine:
                         max_tokens=max_tokens, device=device, eps=eps, max_expert_rows=max_expert_rows)
         self._h = C.c_void_p()
         check(_lib.lib().sp_moe_open(C.byref(c), C.byref(self._h)))
+        self._trace = RouteTrace()
 
     # -- lifecycle
     def close(self):
@@ -83,9 +85,21 @@ class MoeEngine:
         y = np.empty_like(x)
         sel = np.empty((n_layers, M, self.cfg["NU"]), np.int32) if want_routing else None
         wts = np.empty((n_layers, M, self.cfg["NU"]), np.float32) if want_routing else None
+        if self._trace.on and sel is None:           # the trace needs the routing even if the caller does not
+            tsel = np.empty((n_layers, M, self.cfg["NU"]), np.int32); twts = np.empty((n_layers, M, self.cfg["NU"]), np.float32)
+        else:
+            tsel, twts = sel, wts
         check(_lib.lib().sp_moe_forward(self._h, layer_first, n_layers, flavour, M, _ptr(x), _ptr(y),
-                                        _ptr(sel), _ptr(wts)))
+                                        _ptr(tsel), _ptr(twts)))
+        self._trace.record(tsel, twts, layer_first)
         return y, sel, wts
+
+    def decode_batch(self, x, layer_first=0, n_layers=None, want_routing=False):
+        """B tokens through the layers in ONE call with one synchronisation, each in the single-token
+        decode arithmetic: the MoE share of the reference's gemma4_kv_decode_batch
+        (src/backends/cuda/cuda_forward.cu:11729-11757), which runs the B tokens as B sequential
+        steps. Row t of the result is bit-identical to forward(x[t:t+1])."""
+        return self.forward(x, layer_first, n_layers, FLAVOUR_DECODE, want_routing)
 
     def forward_dev(self, x, y, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, sel=None, wts=None, stream=None):
         """Device entry: x, y torch CUDA f32 [M][E]; enqueues on `stream` (a torch stream; default
@@ -113,21 +127,24 @@ class MoeEngine:
                                              rows.data_ptr(), _ptr(sel), _ptr(wts), st))
         return sel_asc, cw, rows
 
-    def ep_experts(self, layer, rows, offsets, flavour=FLAVOUR_PREFILL):
-        """rows torch CUDA f32 [R][E] sorted by expert, offsets int32 [NE+1] -> the experts' outputs [R][E]."""
+    def ep_experts(self, layer, rows, offsets, flavour=FLAVOUR_PREFILL, row_index=None):
+        """rows torch CUDA f32 [R][E], offsets int32 [NE+1]; sorted position p is row row_index[p]
+        (int32; None = rows already sorted by expert) -> the experts' outputs, same row order as `rows`."""
         import torch
         out = torch.empty_like(rows)
         st = torch.cuda.current_stream(rows.device).cuda_stream
-        check(_lib.lib().sp_moe_ep_experts_dev(self._h, layer, flavour, rows.shape[0], rows.data_ptr(), offsets.data_ptr(),
-                                               out.data_ptr(), st))
+        check(_lib.lib().sp_moe_ep_experts_dev(self._h, layer, flavour, rows.shape[0], rows.data_ptr(), _ptr(row_index),
+                                               offsets.data_ptr(), out.data_ptr(), st))
         return out
 
-    def ep_finish(self, layer, x, pair_rows):
-        """x [M][E], pair_rows [M][NU][E] (each token's expert outputs, ascending expert id) -> y [M][E]."""
+    def ep_finish(self, layer, x, pair_rows, pair_index=None):
+        """x [M][E]; token t's k-th expert output (ascending expert id) is row pair_index[t*NU+k] of
+        pair_rows (int32; None = row t*NU+k) -> y [M][E]."""
         import torch
         y = torch.empty_like(x)
         st = torch.cuda.current_stream(x.device).cuda_stream
-        check(_lib.lib().sp_moe_ep_finish_dev(self._h, layer, x.shape[0], x.data_ptr(), pair_rows.data_ptr(), y.data_ptr(), st))
+        check(_lib.lib().sp_moe_ep_finish_dev(self._h, layer, x.shape[0], x.data_ptr(), pair_rows.data_ptr(), _ptr(pair_index),
+                                              y.data_ptr(), st))
         return y
 
 

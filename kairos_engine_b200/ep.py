@@ -66,19 +66,18 @@ class ExpertParallelMoe:
         recv_rows = torch.empty((R, E), dtype=rows.dtype, device=x.device)
         self._a2a(recv_e, send_e, rc, sc)
         self._a2a(recv_rows, send_rows, rc, sc)
-        # rows arrive grouped by source rank, each group sorted by expert: one stable sort by expert
-        order2 = torch.argsort(recv_e.to(torch.int64), stable=True)
-        sorted_rows = recv_rows[order2].contiguous()
+        # rows arrive grouped by source rank, each group sorted by expert: the expert stage walks them
+        # through one stable sort by expert (an index list; the rows themselves stay where they landed)
+        order2 = torch.argsort(recv_e.to(torch.int64), stable=True).to(torch.int32)
         off = expert_offsets(recv_e, NE)
         self.last_rows = R
-        out_sorted = self.engine.ep_experts(L, sorted_rows, off, flavour)
-        out_recv = torch.empty_like(out_sorted)
-        out_recv[order2] = out_sorted
+        out_recv = self.engine.ep_experts(L, recv_rows, off, flavour, row_index=order2)
         back = torch.empty((M * NU, E), dtype=rows.dtype, device=x.device)
         self._a2a(back, out_recv, sc, rc)
-        pair_rows = torch.empty_like(back)
-        pair_rows[order] = back
-        return self.engine.ep_finish(L, x, pair_rows.view(M, NU, E))
+        # back[i] is pair order[i]: the finish stage reads pair p at row inv[p]
+        inv = torch.empty(M * NU, dtype=torch.int32, device=x.device)
+        inv[order] = torch.arange(M * NU, dtype=torch.int32, device=x.device)
+        return self.engine.ep_finish(L, x, back, pair_index=inv)
 
     def forward(self, x, layer_first=0, n_layers=1, flavour=1):
         for L in range(layer_first, layer_first + n_layers):

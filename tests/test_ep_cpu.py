@@ -31,21 +31,27 @@ class FakeStages:
         cw = torch.softmax(torch.gather(s, 1, sel_asc.to(torch.int64)), dim=1)
         return sel_asc, cw, x * 2.0
 
-    def ep_experts(self, L, rows, offsets, flavour):
+    def ep_experts(self, L, rows, offsets, flavour, row_index=None):
         out = torch.empty_like(rows)
         off = offsets.tolist()
         assert off[0] == 0 and off[-1] == rows.shape[0]
+        idx = torch.arange(rows.shape[0]) if row_index is None else row_index.to(torch.int64)
         for e in range(self.cfg["NE"]):
             if off[e + 1] > off[e]:
                 if self.owned is not None:
                     assert e in self.owned, f"expert {e} reached a rank that does not own it"
                 self.seen.append(e)
-                out[off[e]:off[e + 1]] = rows[off[e]:off[e + 1]] * (e + 1) + e
+                sel = idx[off[e]:off[e + 1]]
+                out[sel] = rows[sel] * (e + 1) + e
         return out
 
-    def ep_finish(self, L, x, pair_rows):
+    def ep_finish(self, L, x, pair_rows, pair_index=None):
         sel_asc, cw, _ = self.ep_route(L, x, 0)
-        return x + (cw.unsqueeze(-1) * pair_rows).sum(1)
+        M, NU = cw.shape
+        pr = pair_rows.reshape(M * NU, -1)
+        if pair_index is not None:
+            pr = pr[pair_index.to(torch.int64)]
+        return x + (cw.unsqueeze(-1) * pr.view(M, NU, -1)).sum(1)
 
 
 def single_process(x, n_layers):

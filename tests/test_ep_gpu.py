@@ -62,6 +62,25 @@ def test_experts_stage_accepts_a_subset_and_empty_input():
     eng.close()
 
 
+@pytest.mark.parametrize("flavour", [A, B])
+def test_experts_stage_with_row_index_equals_sorted_rows(flavour):
+    import torch
+    from kairos_engine_b200 import ep
+    cfg = orc.SMALL
+    eng, _ = make_stack(cfg, 1, seed=33, max_tokens=16)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    R = 40
+    rows = torch.randn(R, cfg["E"], device="cuda", generator=g)
+    ids = torch.randint(0, cfg["NE"], (R,), device="cuda", generator=g).to(torch.int32)      # arrival order: unsorted
+    order = torch.argsort(ids.to(torch.int64), stable=True).to(torch.int32)
+    off = ep.expert_offsets(ids, cfg["NE"])
+    out_idx = eng.ep_experts(0, rows, off, flavour, row_index=order)                        # rows stay where they are
+    out_sorted = eng.ep_experts(0, rows[order.long()].contiguous(), off, flavour)
+    eng.status()
+    assert torch.equal(out_idx[order.long()].view(torch.int32), out_sorted.view(torch.int32))
+    eng.close()
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
     return p
