@@ -142,6 +142,25 @@ int gemma4_moe_ffn_q4b_cuda(int E, int NE, int NU, int FF, float eps,
                             const unsigned char *dn_codes, const unsigned short *dn_bscale,
                             const float *hidden, float *out, int *sel_out);
 
+/* The reference's MoE plugin hook for SwiGLU models with separate gate / up / down expert tensors
+ * (sp_q36gpu_upload_experts + sp_q36gpu_moe, CF:16203-16289; the hook type it is registered under
+ * is int (*)(void *ctx, const char *gate_name, const int *idx, const float *wt, int NU,
+ * const float *x, int E, int FF, float *y), CF:16444-16454). Experts are uploaded once per layer
+ * under a tag (HOST pointers; Q4B codes [NE][FF][E/2] + f16 scales for gate and up, [NE][E][FF/2]
+ * + scales for down). sp_moe_ext_moe takes the expert ids and weights the caller's router chose
+ * and HOST x / y: y = sum_k wt[k] * down(silu(gate x) * (up x)) in the caller's k order, in the
+ * decode arithmetic (gemv_w_packed). Returns 0 = handled, nonzero = not mine (unknown tag, other
+ * shape), which is the hook's contract; upload/open return 0 or 1 like the reference's. */
+typedef struct sp_moe_ext sp_moe_ext;
+int sp_moe_ext_open(int device, sp_moe_ext **out);
+int sp_moe_ext_close(sp_moe_ext *h);
+int sp_moe_ext_upload_experts(sp_moe_ext *h, const char *tag,
+                              const uint8_t *gate_codes, const uint16_t *gate_bs,
+                              const uint8_t *up_codes, const uint16_t *up_bs,
+                              const uint8_t *down_codes, const uint16_t *down_bs, int NE, int FF, int E);
+int sp_moe_ext_moe(void *h, const char *tag, const int *idx, const float *wt, int NU,
+                   const float *x, int E, int FF, float *y);
+
 /* Q4B block quantiser on DEVICE memory: the recipe of sp_model.h:50-53 / CF:1680-1687 (per-32
  * block, f16 scale stored first, codes derived against the stored scale, codes in [-7,7]).
  * The reference's own quantiser is in a submodule that is not part of its tree; this follows

@@ -148,6 +148,36 @@ class MoeEngine:
         return y
 
 
+class MoeExt:
+    """The reference's MoE plugin hook (SwiGLU experts, separate gate/up/down tensors, host router):
+    sp_q36gpu_upload_experts / sp_q36gpu_moe of src/backends/cuda/cuda_forward.cu:16203-16289."""
+
+    def __init__(self, device=0):
+        self._h = C.c_void_p()
+        if _lib.lib().sp_moe_ext_open(device, C.byref(self._h)) != 0:
+            raise _lib.SpMoeError(1, (_lib.lib().sp_last_error() or b"").decode())
+
+    def upload_experts(self, tag, gate, gate_bs, up, up_bs, down, down_bs, NE, FF, E):
+        """numpy arrays in the reference's layouts (codes uint8, scales uint16 holding f16 bits)."""
+        arrs = [np.ascontiguousarray(a) for a in (gate, gate_bs, up, up_bs, down, down_bs)]
+        if _lib.lib().sp_moe_ext_upload_experts(self._h, tag.encode(), *[a.ctypes.data for a in arrs], NE, FF, E) != 0:
+            raise _lib.SpMoeError(1, (_lib.lib().sp_last_error() or b"").decode())
+
+    def moe(self, tag, idx, wt, x, FF):
+        """Returns y [E], or None when the hook answers "not mine"."""
+        idx = np.ascontiguousarray(idx, np.int32); wt = np.ascontiguousarray(wt, np.float32); x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        rc = _lib.lib().sp_moe_ext_moe(self._h, tag.encode(), idx.ctypes.data, wt.ctypes.data, idx.size, x.ctypes.data, x.size, FF, y.ctypes.data)
+        return y if rc == 0 else None
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().sp_moe_ext_close(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+
 def q4b_quantize(w):
     """torch CUDA f32 [rows][cols] -> (codes uint8 [rows][cols/2], scales int16-view f16 [rows][cols/32])."""
     import torch
