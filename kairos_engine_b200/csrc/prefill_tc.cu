@@ -14,11 +14,15 @@
  * and D += w_hi*x_hi + w_lo*x_hi + w_hi*x_lo accumulates in fp32 in tensor memory (the dropped
  * w_lo*x_lo term is below 2^-22 relative). That is three MMAs per k-step.
  *
- * Tile: 256 weight rows (two 128-row accumulators) x up to 128 activation rows, K in stages of 64.
- *   gate|up GEMM : accumulator 0 = 128 gate rows, accumulator 1 = the matching 128 up rows, so the
- *                  epilogue thread that owns TMEM lane i holds g and u of the same output and
- *                  writes gelu(g)*u directly, already split into fp16 hi/lo for the next GEMM;
- *   down GEMM    : accumulators = rows [j0, j0+128) and [j0+128, j0+256), fp32 out.
+ * Tile: 128 activation rows (the MMA's M: one TMEM lane per row) x 256 weight rows (its N: one
+ * TMEM column per weight row), K in stages of 64. One 128x256x16 MMA reads 12 KB of operands from
+ * shared memory per 128 tensor-core cycles; two 128x128x16 ones would read 16 KB, and shared-memory
+ * bandwidth (operand reads + the unpack warps' writes + TMA) is what bounds this kernel.
+ *   gate|up GEMM : columns [0,128) = 128 gate rows, columns [128,256) = the matching 128 up rows, so
+ *                  the epilogue thread that owns a TMEM lane (one activation row) holds g and u of
+ *                  the same outputs and writes gelu(g)*u directly, already split into fp16 hi/lo
+ *                  for the next GEMM, 16 bytes at a time;
+ *   down GEMM    : columns = weight rows [j0, j0+256), fp32 out, 16 bytes at a time.
  * Activation tiles come in by TMA (2-D tiled copy, 128-byte swizzle) from row lists sorted by
  * expert; weight tiles are unpacked by eight warps into the same swizzled layout. Inside every
  * group of 8 k the order is 0,4,1,5,2,6,3,7 on BOTH operands (the natural order of the nibble
@@ -108,6 +112,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ int kpos(int e) { return ((e & 3) << 1) | (e >> 2); }     /* slot of element e inside its group of 8 */
 
 /* one Q4B block (32 weights, one f16 scale) -> four 16-byte chunks of hi and of lo halves */
@@ -193,9 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
             uint32_t it = 0, lt = 0;
             for (int w = blockIdx.x; w < total && !failed; w += gridDim.x, lt++) {
                 const int nt = w / a.m_tiles;
-                const int nv = a.tiles[3 * nt + 2];
-                const uint32_t N = (uint32_t)((nv + 15) & ~15);
-                const uint32_t idesc = (1u << 4) | ((N >> 3) << 17) | ((128u >> 4) << 24);     /* f16 x f16 -> f32, K-major both, M = 128 */
+                const uint32_t idesc = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);   /* f16 x f16 -> f32, K-major both, M = 128, N = 256 */
                 const int b = lt & 1; const uint32_t bph = (lt >> 1) & 1;
                 if (!mbar_wait(tempty(b), bph ^ 1, abort_flag)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -206,16 +215,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st = sbase + s * kStageBytes;
 #pragma unroll
-                    for (int acc = 0; acc < 2; acc++) {
-#pragma unroll
-                        for (int ks = 0; ks < kBK / 16; ks++) {
-                            const uint64_t ahi = make_desc(st + acc * 16384 + ks * 32), alo = make_desc(st + kAHalf + acc * 16384 + ks * 32);
-                            const uint64_t bhi = make_desc(st + 2 * kAHalf + ks * 32), blo = make_desc(st + 2 * kAHalf + kBHalf + ks * 32);
-                            const uint32_t d = d0 + acc * 128;
-                            umma_f16(d, ahi, bhi, idesc, (kb | ks) ? 1u : 0u);
-                            umma_f16(d, alo, bhi, idesc, 1u);
-                            umma_f16(d, ahi, blo, idesc, 1u);
-                        }
+                    for (int ks = 0; ks < kBK / 16; ks++) {
+                        /* A operand = activation rows (M), B operand = the 256 weight rows (N) */
+                        const uint64_t whi = make_desc(st + ks * 32), wlo = make_desc(st + kAHalf + ks * 32);
+                        const uint64_t xhi = make_desc(st + 2 * kAHalf + ks * 32), xlo = make_desc(st + 2 * kAHalf + kBHalf + ks * 32);
+                        umma_f16(d0, xhi, whi, idesc, (kb | ks) ? 1u : 0u);
+                        umma_f16(d0, xhi, wlo, idesc, 1u);
+                        umma_f16(d0, xlo, whi, idesc, 1u);
                     }
                     umma_commit(empty(s));                          /* stage reusable once these MMAs have read it */
                 }
@@ -255,7 +261,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
         }
     } else {
         /* ---------------- epilogue: TMEM -> registers -> global */
-        const int i = warp * 32 + lane;                             /* TMEM lane = row inside each accumulator */
+        const int i = warp * 32 + lane;                             /* TMEM lane = activation row inside the tile */
         uint32_t lt = 0;
         for (int w = blockIdx.x; w < total && !failed; w += gridDim.x, lt++) {
             const int nt = w / a.m_tiles, mt = w - nt * a.m_tiles;
@@ -264,36 +270,48 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
             if (!mbar_wait(tfull(b), bph, abort_flag)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t t0 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * 256);
-            for (int c0 = 0; c0 < nv; c0 += 32) {
-                uint32_t g[32], u[32];
-                tmem_ld32(t0 + c0, g);
-                tmem_ld32(t0 + 128 + c0, u);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (PAIR) {
-                    const int j = mt * 128 + i;
-                    if (j < a.rows) {
-                        const size_t col = (size_t)(j & ~7) + kpos(j & 7);
+            const bool rv = i < nv;
+            const int sr = row0 + (rv ? i : 0);
+            if (PAIR) {
+                __half *ohi = a.out_hi + (size_t)sr * a.out_k, *olo = a.out_lo + (size_t)sr * a.out_k;
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    const int j0 = mt * 128 + c0;
+                    if (j0 >= a.rows) break;                             /* warp-uniform */
+                    uint32_t g[16], u[16];
+                    tmem_ld16(t0 + c0, g);
+                    tmem_ld16(t0 + 128 + c0, u);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (rv) {
 #pragma unroll
-                        for (int n = 0; n < 32; n++) {
-                            if (c0 + n < nv) {
-                                const float h = gelu_mul(__uint_as_float(g[n]), __uint_as_float(u[n]));
-                                const __half hh = __float2half_rn(h);
-                                const __half hl = __float2half_rn(__fsub_rn(h, __half2float(hh)));
-                                const size_t o = (size_t)(row0 + c0 + n) * a.out_k + col;
-                                a.out_hi[o] = hh; a.out_lo[o] = hl;
+                        for (int h8 = 0; h8 < 2; h8++) {
+                            if (j0 + 8 * h8 < a.rows) {                  /* rows is a multiple of 8 */
+                                __half hh[8], hl[8];
+#pragma unroll
+                                for (int n = 0; n < 8; n++) {
+                                    const float h = gelu_mul(__uint_as_float(g[8 * h8 + n]), __uint_as_float(u[8 * h8 + n]));
+                                    const __half x = __float2half_rn(h);
+                                    hh[kpos(n)] = x; hl[kpos(n)] = __float2half_rn(__fsub_rn(h, __half2float(x)));
+                                }
+                                *reinterpret_cast<uint4 *>(ohi + j0 + 8 * h8) = *reinterpret_cast<const uint4 *>(hh);
+                                *reinterpret_cast<uint4 *>(olo + j0 + 8 * h8) = *reinterpret_cast<const uint4 *>(hl);
                             }
                         }
                     }
-                } else {
-                    const int j0 = mt * 256 + i, j1 = j0 + 128;
+                }
+            } else {
+                float *orow = a.out_f + (size_t)(a.rowmap ? __ldg(a.rowmap + sr) : sr) * a.out_stride;
+                for (int c0 = 0; c0 < 256; c0 += 16) {
+                    const int j0 = mt * 256 + c0;
+                    if (j0 >= a.rows) break;                             /* warp-uniform */
+                    uint32_t v[16];
+                    tmem_ld16(t0 + c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (rv) {
 #pragma unroll
-                    for (int n = 0; n < 32; n++) {
-                        if (c0 + n < nv) {
-                            const int sr = row0 + c0 + n;
-                            const size_t orow = (size_t)(a.rowmap ? __ldg(a.rowmap + sr) : sr) * a.out_stride;
-                            if (j0 < a.rows) a.out_f[orow + j0] = __uint_as_float(g[n]);
-                            if (j1 < a.rows) a.out_f[orow + j1] = __uint_as_float(u[n]);
-                        }
+                        for (int q = 0; q < 4; q++)
+                            if (j0 + 4 * q < a.rows)                     /* rows is a multiple of 4 */
+                                *reinterpret_cast<float4 *>(orow + j0 + 4 * q) =
+                                    make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
                     }
                 }
             }
