@@ -148,6 +148,33 @@ def run_reference(args, rank, world):
         dist.barrier(); dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------- batched decode / draft-verify shapes
+def small_batch_leg(eng, NL, local_rank, rank):
+    """M in {4, 8, 16, 64} tokens per step through the stack in the single-token decode arithmetic
+    (what M sequential decode steps compute), unbiased router: the union of active experts grows with M."""
+    import torch
+    from kairos_engine_b200 import FLAVOUR_DECODE, synth
+    out = {}
+    for M in (4, 8, 16, 64):
+        if M > eng.max_tokens:
+            continue
+        x = synth.make_inputs(CFG, M, seed=300 + M + rank, device=f"cuda:{local_rank}")
+        y = torch.empty_like(x)
+        for _ in range(3):
+            eng.forward_dev(x, y, 0, NL, FLAVOUR_DECODE)
+        eng.status()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            eng.forward_dev(x, y, 0, NL, FLAVOUR_DECODE)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        out[f"M={M}"] = {"tokens_per_s": M / (ms / 1e3), "ms_per_step": ms}
+    return out
+
+
 # ---------------------------------------------------------------- prefill (reported beside the decode metric)
 def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     """PT tokens through the stack in the prefill arithmetic: one GPU runs them all; N GPUs run
@@ -276,6 +303,7 @@ def run_ours(args, rank, local_rank, world):
     e2e_v = T * e2e_steps * world / e2e_s
 
     prefill = prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier) if PT else None
+    small = small_batch_leg(eng, NL, local_rank, rank) if (PT and world == 1) else None
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -295,6 +323,8 @@ def run_ours(args, rank, local_rank, world):
                 "gpu_launches": int(launches), "clocks": clk.summary()}
         if prefill:
             line["prefill"] = prefill
+        if small:
+            line["small_batch"] = small
         if world == 1 and not args.no_cpu:
             try:
                 threads = min(os.cpu_count() or 1, 16)

@@ -66,6 +66,9 @@ struct sp_moe {
     /* three-kernel decode path replayed from CUDA graphs, one per (first layer, layer count) */
     struct DecodeGraph { int lf, nl; bool routing; cudaGraphExec_t exec; int launches; };
     std::vector<DecodeGraph> graphs;
+    /* small batches (1 < M <= 64) are launch-bound: the layer run is replayed from a graph per shape */
+    struct BatchGraph { int lf, nl, M, flavour; bool routing; cudaGraphExec_t exec; int launches; };
+    std::vector<BatchGraph> bgraphs;
     SpGraphScratch gs; unsigned char *gs_base; float *g_x, *g_y; int32_t *g_sel; float *g_wts;
     int decode_impl;            /* 0 = CUDA graph of three kernels per layer, 1 = one persistent kernel */
     int sms;
@@ -199,6 +202,7 @@ extern "C" int sp_moe_close(sp_moe *h) {
     if (h->stream) { cudaStreamSynchronize(h->stream); cudaStreamDestroy(h->stream); }
     sp_batched_free(&h->bs);
     for (auto &g : h->graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
+    for (auto &g : h->bgraphs) if (g.exec) cudaGraphExecDestroy(g.exec);
     void *ps[] = {h->gs_base, h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
     for (void *p : ps) if (p) cudaFree(p);
     cudaGetLastError();
@@ -310,6 +314,35 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
         h->launches += 1;
         xin = y_dev;
         }
+        return SP_MOE_OK;
+    }
+    if (M <= 64) {
+        const bool routing = sel_dev || wts_dev;
+        sp_moe::BatchGraph *bg = nullptr;
+        for (auto &g : h->bgraphs) if (g.lf == lf && g.nl == nl && g.M == M && g.flavour == flavour && g.routing == routing) bg = &g;
+        if (!bg) {
+            if (h->bgraphs.size() >= 32) { cudaGraphExecDestroy(h->bgraphs.front().exec); h->bgraphs.erase(h->bgraphs.begin()); }
+            cudaStream_t cs = h->stream;
+            cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr; int nlaunch = 0;
+            CK(cudaStreamSynchronize(cs), "stream synchronize");
+            CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal), "begin capture");
+            cudaError_t e = sp_batched_forward(h->d, h->layers_host.data(), lf, nl, flavour, M, h->x_dev, h->y_dev, routing ? h->sel_dev : nullptr,
+                                               routing ? h->wts_dev : nullptr, &h->bs, h->status, cs, &nlaunch);
+            cudaError_t e2 = cudaStreamEndCapture(cs, &graph);
+            if (e != cudaSuccess || e2 != cudaSuccess) { if (graph) cudaGraphDestroy(graph); cudaGetLastError(); return fail_cuda(e != cudaSuccess ? e : e2, "batched graph capture"); }
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return fail_cuda(e, "batched graph instantiate");
+            h->bgraphs.push_back({lf, nl, M, flavour, routing, exec, nlaunch});
+            bg = &h->bgraphs.back();
+        }
+        const size_t nb = (size_t)M * h->cfg.E * 4, ns = (size_t)nl * M * h->cfg.NU * 4;
+        if (x_dev != h->x_dev) CK(cudaMemcpyAsync(h->x_dev, x_dev, nb, cudaMemcpyDeviceToDevice, st), "x staging");
+        CK(cudaGraphLaunch(bg->exec, st), "batched graph launch");
+        if (y_dev != h->y_dev) CK(cudaMemcpyAsync(y_dev, h->y_dev, nb, cudaMemcpyDeviceToDevice, st), "y staging");
+        if (sel_dev && sel_dev != h->sel_dev) CK(cudaMemcpyAsync(sel_dev, h->sel_dev, ns, cudaMemcpyDeviceToDevice, st), "sel staging");
+        if (wts_dev && wts_dev != h->wts_dev) CK(cudaMemcpyAsync(wts_dev, h->wts_dev, ns, cudaMemcpyDeviceToDevice, st), "wts staging");
+        h->launches += (uint64_t)bg->launches;
         return SP_MOE_OK;
     }
     int nlaunch = 0;
