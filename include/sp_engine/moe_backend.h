@@ -161,6 +161,17 @@ int sp_moe_ext_upload_experts(sp_moe_ext *h, const char *tag,
 int sp_moe_ext_moe(void *h, const char *tag, const int *idx, const float *wt, int NU,
                    const float *x, int E, int FF, float *y);
 
+/* The quantised GEMM of src/backends/cuda/ptx_mma.cuh (sp_frob_matmul_q8_mma_tile, ptx_mma_tile_int8.cuh:92-110,
+ * and the int4 kernels, ptx_mma.cuh:268-353) on DEVICE memory:
+ *   C[m][n] (f16 bits) = f16( float(sum_k A[m][k] * B[n][k]) * scale_a[m] * scale_b[n] ),
+ * A [M][K] and B [N][K] int8 (q8) or packed signed int4, two per byte, low nibble first (q4);
+ * int32 accumulate; K a multiple of 16, operand pointers 16-byte aligned. Enqueues on `stream`;
+ * the q4 entry unpacks into scratch it allocates, so it also synchronises the stream and frees. */
+int sp_frob_matmul_q8_dev(const int8_t *A_dev, const int8_t *B_dev, const float *scale_a_dev,
+                          const float *scale_b_dev, uint16_t *C_f16_dev, int M, int K, int N, void *stream);
+int sp_frob_matmul_q4_dev(const uint8_t *A_q4_dev, const uint8_t *B_q4_dev, const float *scale_a_dev,
+                          const float *scale_b_dev, uint16_t *C_f16_dev, int M, int K, int N, void *stream);
+
 /* Q4B block quantiser on DEVICE memory: the recipe of sp_model.h:50-53 / CF:1680-1687 (per-32
  * block, f16 scale stored first, codes derived against the stored scale, codes in [-7,7]).
  * The reference's own quantiser is in a submodule that is not part of its tree; this follows

@@ -218,3 +218,17 @@ def gemv_q4b(codes, bs, x):
     check(_lib.lib().sp_moe_gemv_q4b_dev(codes.data_ptr(), bs.data_ptr(), cols, rows, x.contiguous().data_ptr(), y.data_ptr(),
                                          torch.cuda.current_stream(codes.device).cuda_stream))
     return y
+
+
+def int_gemm_scaled(A, B, scale_a, scale_b, packed_int4=False):
+    """The reference's quantised GEMM (ptx_mma.cuh): torch CUDA tensors A [M][K], B [N][K] int8 (or uint8
+    [.][K/2] packed signed int4), scales f32 [M], [N] -> C f16 [M][N] = f16(float(A.B^T) * sa[m] * sb[n])."""
+    import torch
+    A, B = A.contiguous(), B.contiguous()
+    M, N = A.shape[0], B.shape[0]
+    K = A.shape[1] * (2 if packed_int4 else 1)
+    Cc = torch.empty((M, N), dtype=torch.float16, device=A.device)
+    fn = _lib.lib().sp_frob_matmul_q4_dev if packed_int4 else _lib.lib().sp_frob_matmul_q8_dev
+    check(fn(A.data_ptr(), B.data_ptr(), scale_a.contiguous().data_ptr(), scale_b.contiguous().data_ptr(), Cc.data_ptr(), M, K, N,
+             torch.cuda.current_stream(A.device).cuda_stream))
+    return Cc

@@ -165,6 +165,15 @@ def q4b_quantize(w):
     return codes, bs
 
 
+def int_gemm_scaled(A, B, scale_a, scale_b):
+    """A [M][K], B [N][K] int8 -> C [M][N] f16 bits (uint16): f16(float(A.B^T) * sa[m] * sb[n])."""
+    A = np.ascontiguousarray(A, np.int8); B = np.ascontiguousarray(B, np.int8)
+    M, K = A.shape; N = B.shape[0]
+    Cq = np.empty((M, N), np.uint16)
+    lib().orc_int_gemm_scaled(p(A, i8p), p(B, i8p), M, N, K, p(c32(scale_a), f32p), p(c32(scale_b), f32p), p(Cq, u16p))
+    return Cq
+
+
 def q4b_dequantize(codes, bs):
     rows, cols = codes.shape[0], codes.shape[1] * 2
     w = np.empty((rows, cols), np.float32)
