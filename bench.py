@@ -175,6 +175,31 @@ def small_batch_leg(eng, NL, local_rank, rank):
     return out
 
 
+# ---------------------------------------------------------------- the quantised (int8 x int8 -> f16) GEMM
+def int_gemm_leg(local_rank):
+    import torch
+    from kairos_engine_b200.engine import int_gemm_scaled
+    M = N = K = 8192
+    dev = f"cuda:{local_rank}"
+    g = torch.Generator(device=dev).manual_seed(11)
+    A = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+    B = torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+    sa = torch.rand(M, device=dev, generator=g) * 1e-3
+    sb = torch.rand(N, device=dev, generator=g) * 1e-3
+    for _ in range(3):
+        int_gemm_scaled(A, B, sa, sb)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        int_gemm_scaled(A, B, sa, sb)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"shape": [M, N, K], "ms": ms, "tops": 2.0 * M * N * K / (ms / 1e3) / 1e12,
+            "note": "tcgen05 kind::i8, int32 accumulate in TMEM, f16 out with per-row x per-column scales"}
+
+
 # ---------------------------------------------------------------- prefill (reported beside the decode metric)
 def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     """PT tokens through the stack in the prefill arithmetic: one GPU runs them all; N GPUs run
@@ -304,6 +329,7 @@ def run_ours(args, rank, local_rank, world):
 
     prefill = prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier) if PT else None
     small = small_batch_leg(eng, NL, local_rank, rank) if (PT and world == 1) else None
+    igemm = int_gemm_leg(local_rank) if (PT and world == 1) else None
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -325,6 +351,8 @@ def run_ours(args, rank, local_rank, world):
             line["prefill"] = prefill
         if small:
             line["small_batch"] = small
+        if igemm:
+            line["int_gemm"] = igemm
         if world == 1 and not args.no_cpu:
             try:
                 threads = min(os.cpu_count() or 1, 16)
