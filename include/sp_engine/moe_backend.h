@@ -113,8 +113,11 @@ int  sp_moe_status(sp_moe *h);
  * handle (the shared-expert branch and the combine weights wait in the handle between route and
  * finish).
  *   route   : x[M][E] -> sel_asc[M][NU] (each token's experts, ascending id), cw[M][NU] (combine
- *             weight = renormalised probability * down-scale, same order), rows[M][E] (the routed
- *             experts' input: x normalised with pre_ffw_norm_2); sel/wts as in sp_moe_forward (or NULL)
+ *             weight = renormalised probability * down-scale, same order), rows[M*NU][E] (each
+ *             pair's input row - x normalised with pre_ffw_norm_2 - sorted by expert, so by owner:
+ *             the all-to-all send buffer), counts[NE] (pairs per expert), pair_index[M*NU] (the row
+ *             of pair t*NU+k in that buffer, and so in what comes back); sel/wts as in
+ *             sp_moe_forward (or NULL)
  *   experts : rows_in[n_rows][E] -> rows_out[n_rows][E] = down(geglu(gate|up(row))) with the weights of
  *             the row's expert. Sorted by expert, position p belongs to expert e when
  *             offsets[e] <= p < offsets[e+1] (offsets: NE+1 ints, device memory) and is row
@@ -124,8 +127,8 @@ int  sp_moe_status(sp_moe *h);
  *             (pair_index NULL = row t*NU+k) -> y = the layer's output residual
  * A run through the three stages is bit-identical to sp_moe_forward_dev on the same tokens. */
 int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,
-                        int32_t *sel_asc_dev, float *cw_dev, float *rows_dev,
-                        int32_t *sel_dev, float *wts_dev, void *stream);
+                        int32_t *sel_asc_dev, float *cw_dev, float *rows_dev, int32_t *counts_dev,
+                        int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, void *stream);
 int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev,
                           const int32_t *row_index_dev, const int32_t *offsets_dev, float *rows_out_dev,
                           void *stream);

@@ -71,7 +71,7 @@ def lib():
         L.sp_moe_gemv_q4b_static_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.sp_moe_gelu_mul_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         L.sp_moe_kernel_launches.argtypes = [C.c_void_p]
-        L.sp_moe_ep_route_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 7
+        L.sp_moe_ep_route_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 9
         L.sp_moe_ep_experts_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 5
         L.sp_moe_ep_finish_dev.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 5
         L.sp_moe_kernel_launches.restype = C.c_uint64

@@ -26,7 +26,7 @@ struct BView {                 /* carved scratch */
     signed char *nx_q, *in_q, *hd_q, *h_q;
     float *nx_s, *in_s, *hd_s, *h_s;
     int *nx_c, *in_c, *hd_c, *h_c;
-    int *sel_asc, *count, *list, *pairpos;
+    int *sel_asc, *count, *list, *pairpos, *ep_off;
     signed char *ep_q; float *ep_s; int *ep_c;      /* expert-parallel stage: quantised received rows, [max_rows] */
 };
 
@@ -45,11 +45,11 @@ size_t blayout(const SpDims &d, int Mx, int Rx, F place) {
     take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * R * (FFE / 16));        /* c */
     take(4 * M * NU); take(4 * NE); take(4 * NE * M);                                               /* sel_asc count list */
     take(R * E); take(4 * R * (E / 16)); take(4 * R * (E / 16));                                    /* ep_q ep_s ep_c */
-    take(4 * M * NU);                                                                               /* pairpos */
+    take(4 * M * NU); take(4 * (NE + 1));                                                           /* pairpos ep_off */
     return o;
 }
 BView bview(const SpDims &d, const SpBatchedScratch *s) {
-    unsigned char *p[30];
+    unsigned char *p[31];
     blayout(d, s->max_tokens, s->max_rows, [&](int id, size_t off) { p[id] = (unsigned char *)s->base + off; });
     BView v;
     v.rin = (float *)p[0]; v.nx_f = (float *)p[1]; v.in_f = (float *)p[2]; v.logits = (float *)p[3]; v.cw = (float *)p[4];
@@ -58,7 +58,7 @@ BView bview(const SpDims &d, const SpBatchedScratch *s) {
     v.nx_s = (float *)p[15]; v.in_s = (float *)p[16]; v.hd_s = (float *)p[17]; v.h_s = (float *)p[18];
     v.nx_c = (int *)p[19]; v.in_c = (int *)p[20]; v.hd_c = (int *)p[21]; v.h_c = (int *)p[22];
     v.sel_asc = (int *)p[23]; v.count = (int *)p[24]; v.list = (int *)p[25];
-    v.ep_q = (signed char *)p[26]; v.ep_s = (float *)p[27]; v.ep_c = (int *)p[28]; v.pairpos = (int *)p[29];
+    v.ep_q = (signed char *)p[26]; v.ep_s = (float *)p[27]; v.ep_c = (int *)p[28]; v.pairpos = (int *)p[29]; v.ep_off = (int *)p[30];
     return v;
 }
 
@@ -458,6 +458,27 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
     return cudaGetLastError();
 }
 
+/* per-expert counts -> exclusive offsets (NE is at most 1024: one block) */
+__global__ void __launch_bounds__(1024) k_b_scan(const int *count, int n, int *off) {
+    __shared__ int sh[1024];
+    const int t = threadIdx.x;
+    sh[t] = t < n ? count[t] : 0;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) { const int v = t >= d ? sh[t - d] : 0; __syncthreads(); sh[t] += v; __syncthreads(); }
+    if (t < n) off[t + 1] = sh[t];
+    if (t == 0) off[0] = 0;
+}
+/* one block per (token, expert) pair: its input row goes to position off[e] + pairpos of the send buffer */
+__global__ void __launch_bounds__(256) k_b_dispatch_rows(const float *in_f, const int *sel_asc, const int *pairpos, const int *off, int NU, int E,
+                                                         float *rows, int *pair_index) {
+    const int p = blockIdx.x;
+    const int pos = off[sel_asc[p]] + pairpos[p];
+    if (threadIdx.x == 0) pair_index[p] = pos;
+    const float4 *src = reinterpret_cast<const float4 *>(in_f + (size_t)(p / NU) * E);
+    float4 *dst = reinterpret_cast<float4 *>(rows + (size_t)pos * E);
+    for (int i = threadIdx.x; i < E / 4; i += 256) dst[i] = src[i];
+}
+
 /* ---------------------------------------------------------------- expert-parallel stages
  * The layer cut at the two places where (token, expert) pairs change GPU:
  *   route   : norms, router, top-k, the shared expert (kept in this handle's scratch), and the
@@ -467,13 +488,18 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
  *   finish  : ordered combine of the returned pair rows + the recombine.
  * The arithmetic of each pair is the single-GPU batched path's, so a split run is bit-identical. */
 template <bool FA>
-cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows,
-                     int32_t *sel, float *wts, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows, int32_t *counts,
+                     int32_t *pair_index, int32_t *sel, float *wts, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, NU = d.NU, FFS = d.FFS;
-    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, rows); (*nl)++;
+    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, FA ? v.in_f : nullptr); (*nl)++;
     cudaError_t e = cudaSuccess;
     k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
+    /* the send buffer: rows sorted by expert (so also by owner), ready for the all-to-all */
+    k_b_scan<<<1, 1024, 0, st>>>(v.count, NE, v.ep_off); (*nl)++;
+    k_b_dispatch_rows<<<M * NU, 256, 0, st>>>(v.in_f, v.sel_asc, v.pairpos, v.ep_off, NU, E, rows, pair_index); (*nl)++;
+    e = cudaMemcpyAsync(counts, v.count, (size_t)4 * NE, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return e;
     if (!FA && tc) {
         e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
         if (e != cudaSuccess) return e;
@@ -519,12 +545,12 @@ cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float 
 }  // namespace
 
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
-                                float *rows, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
     if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch)
-                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, sel, wts, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, v, s->tc, status, st, nlaunch)
+                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, v, s->tc, status, st, nlaunch);
 }
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {

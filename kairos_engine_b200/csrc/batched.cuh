@@ -22,12 +22,13 @@ cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, i
 /* The same layer cut into the three stages an expert-parallel run needs (one layer at a time;
  * the shared-expert result and the combine weights stay in the scratch between route and finish).
  *   route   : sel_asc[M*NU] (expert ids per token, ascending), cw[M*NU] (combine weights in that
- *             order), rows[M*E] (the routed experts' input rows)
+ *             order), rows[M*NU][E] (each pair's input row, sorted by expert), counts[NE] (pairs per
+ *             expert), pair_index[M*NU] (where pair t*NU+k sits in rows)
  *   experts : R rows; sorted position p (expert e owns positions [offsets[e], offsets[e+1])) is row
  *             row_index[p] of rows_in and of rows_out (NULL = the rows are already sorted); R <= max_rows
  *   finish  : output of token t's k-th expert (ascending id) = pair_rows[pair_index[t*NU+k]] (NULL = t*NU+k) */
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
-                                float *rows, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,

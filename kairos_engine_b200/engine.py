@@ -116,16 +116,19 @@ class MoeEngine:
 
     # -- one layer in three stages (expert-parallel runs move rows between them; see ep.py)
     def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None):
-        """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 [M][E])."""
+        """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 [M*NU][E] sorted by
+        expert, counts int32 [NE], pair_index int32 [M*NU])."""
         import torch
-        M, NU = x.shape[0], self.cfg["NU"]
+        M, NU, NE = x.shape[0], self.cfg["NU"], self.cfg["NE"]
         sel_asc = torch.empty((M, NU), dtype=torch.int32, device=x.device)
         cw = torch.empty((M, NU), dtype=torch.float32, device=x.device)
-        rows = torch.empty_like(x)
+        rows = torch.empty((M * NU, x.shape[1]), dtype=torch.float32, device=x.device)
+        counts = torch.empty(NE, dtype=torch.int32, device=x.device)
+        pair_index = torch.empty(M * NU, dtype=torch.int32, device=x.device)
         st = torch.cuda.current_stream(x.device).cuda_stream
         check(_lib.lib().sp_moe_ep_route_dev(self._h, layer, flavour, M, x.data_ptr(), sel_asc.data_ptr(), cw.data_ptr(),
-                                             rows.data_ptr(), _ptr(sel), _ptr(wts), st))
-        return sel_asc, cw, rows
+                                             rows.data_ptr(), counts.data_ptr(), pair_index.data_ptr(), _ptr(sel), _ptr(wts), st))
+        return sel_asc, cw, rows, counts, pair_index
 
     def ep_experts(self, layer, rows, offsets, flavour=FLAVOUR_PREFILL, row_index=None):
         """rows torch CUDA f32 [R][E], offsets int32 [NE+1]; sorted position p is row row_index[p]

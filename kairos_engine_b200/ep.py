@@ -5,7 +5,7 @@ The reference is single-GPU: its batched branch walks every expert on the one de
 residual of its own tokens, the router, the shared expert and the norms) and the routed experts
 are partitioned contiguously, `NE / world` per rank. Per layer there is one exchange each way:
 
-  route (local) -> dispatch all-to-all of (expert id, input row) per (token, expert) pair
+  route (local) -> all-gather of the per-expert pair counts -> dispatch all-to-all of the input rows
   -> experts (on the owner) -> combine all-to-all of the output rows back -> finish (local).
 
 The per-token combine still walks the experts in ascending id on the home rank, so the result is
@@ -19,7 +19,8 @@ import torch.distributed as dist
 def plan_dispatch(sel_asc, n_experts, world):
     """sel_asc: int [M][NU] expert ids. Returns (order, send_counts): `order` lists the pair
     indices (t*NU + k) sorted by expert id, stably; because ownership is contiguous that is also
-    sorted by destination rank; send_counts[r] = pairs going to rank r."""
+    sorted by destination rank; send_counts[r] = pairs going to rank r. (Reference form of what the
+    route stage does on the device; used by tests.)"""
     per = n_experts // world
     e = sel_asc.reshape(-1).to(torch.int64)
     order = torch.argsort(e, stable=True)
@@ -33,6 +34,28 @@ def expert_offsets(expert_ids, n_experts):
     off = torch.zeros(n_experts + 1, dtype=torch.int32, device=expert_ids.device)
     off[1:] = torch.cumsum(cnt, 0).to(torch.int32)
     return off
+
+
+def recv_layout(counts_all, rank, n_rows):
+    """counts_all: int [world][NE], pairs per expert on every rank. The rows this rank receives arrive
+    source-major (each source's block sorted by expert). Returns (offsets int32 [NE+1], row_index int32
+    [n_rows]): expert e owns sorted positions [offsets[e], offsets[e+1]) and sorted position p is arrival
+    row row_index[p]. No host synchronisation: n_rows is already known from the split sizes."""
+    world, NE = counts_all.shape
+    epr = NE // world
+    dev = counts_all.device
+    c = counts_all[:, rank * epr:(rank + 1) * epr].to(torch.int64)          # [source][my expert]
+    arr = c.reshape(-1)
+    arr_start = (torch.cumsum(arr, 0) - arr).view(world, epr)               # arrival start of block (source, expert)
+    ct = c.t().contiguous().reshape(-1)                                     # block sizes in sorted order (expert, source)
+    sorted_start = torch.cumsum(ct, 0) - ct
+    block = torch.repeat_interleave(torch.arange(world * epr, device=dev), ct, output_size=n_rows)
+    start_of_block = arr_start.t().contiguous().reshape(-1)
+    row_index = (start_of_block[block] + (torch.arange(n_rows, device=dev) - sorted_start[block])).to(torch.int32)
+    offsets = torch.zeros(NE + 1, dtype=torch.int32, device=dev)
+    offsets[rank * epr + 1:(rank + 1) * epr + 1] = torch.cumsum(c.sum(0), 0).to(torch.int32)
+    offsets[(rank + 1) * epr + 1:] = n_rows
+    return offsets, row_index
 
 
 class ExpertParallelMoe:
@@ -52,32 +75,25 @@ class ExpertParallelMoe:
 
     def layer(self, L, x, flavour):
         NE, NU, E = self.cfg["NE"], self.cfg["NU"], self.cfg["E"]
-        M = x.shape[0]
-        sel_asc, cw, rows = self.engine.ep_route(L, x, flavour)
-        order, send_counts = plan_dispatch(sel_asc, NE, self.world)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        # one host read of 2*world integers per layer: the split sizes of the two exchanges
-        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        M, world, epr = x.shape[0], self.world, self.cfg["NE"] // self.world
+        # route: the send buffer comes back already sorted by expert (= by owner)
+        sel_asc, cw, rows, counts, pair_index = self.engine.ep_route(L, x, flavour)
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts, group=self.group)
+        counts_all = torch.stack(gathered)                                   # [world][NE]
+        send_counts = counts.view(world, epr).sum(1)
+        recv_counts = counts_all[:, self.rank * epr:(self.rank + 1) * epr].sum(1)
+        # the one host read of the layer: the split sizes of the two exchanges
+        sc, rc = torch.stack([send_counts, recv_counts]).tolist()
         R = sum(rc)
-        send_e = sel_asc.reshape(-1)[order].contiguous()
-        send_rows = rows[torch.div(order, NU, rounding_mode="floor")].contiguous()
-        recv_e = torch.empty(R, dtype=send_e.dtype, device=x.device)
         recv_rows = torch.empty((R, E), dtype=rows.dtype, device=x.device)
-        self._a2a(recv_e, send_e, rc, sc)
-        self._a2a(recv_rows, send_rows, rc, sc)
-        # rows arrive grouped by source rank, each group sorted by expert: the expert stage walks them
-        # through one stable sort by expert (an index list; the rows themselves stay where they landed)
-        order2 = torch.argsort(recv_e.to(torch.int64), stable=True).to(torch.int32)
-        off = expert_offsets(recv_e, NE)
+        self._a2a(recv_rows, rows, rc, sc)
+        offsets, row_index = recv_layout(counts_all, self.rank, R)
         self.last_rows = R
-        out_recv = self.engine.ep_experts(L, recv_rows, off, flavour, row_index=order2)
+        out_recv = self.engine.ep_experts(L, recv_rows, offsets, flavour, row_index=row_index)
         back = torch.empty((M * NU, E), dtype=rows.dtype, device=x.device)
         self._a2a(back, out_recv, sc, rc)
-        # back[i] is pair order[i]: the finish stage reads pair p at row inv[p]
-        inv = torch.empty(M * NU, dtype=torch.int32, device=x.device)
-        inv[order] = torch.arange(M * NU, dtype=torch.int32, device=x.device)
-        return self.engine.ep_finish(L, x, back, pair_index=inv)
+        return self.engine.ep_finish(L, x, back, pair_index=pair_index)
 
     def forward(self, x, layer_first=0, n_layers=1, flavour=1):
         for L in range(layer_first, layer_first + n_layers):

@@ -24,12 +24,22 @@ class FakeStages:
         self.wr = torch.randn(cfg["E"], cfg["NE"], generator=g)
         self.cfg, self.owned, self.seen = cfg, owned, []
 
-    def ep_route(self, L, x, flavour):
+    def _route(self, L, x):
         s = x @ self.wr + L
         idx = torch.topk(s, self.cfg["NU"], dim=1).indices
         sel_asc = torch.sort(idx, dim=1).values.to(torch.int32)
         cw = torch.softmax(torch.gather(s, 1, sel_asc.to(torch.int64)), dim=1)
-        return sel_asc, cw, x * 2.0
+        return sel_asc, cw
+
+    def ep_route(self, L, x, flavour):
+        sel_asc, cw = self._route(L, x)
+        NU, NE = self.cfg["NU"], self.cfg["NE"]
+        order, _ = ep.plan_dispatch(sel_asc, NE, 1)
+        rows = (x * 2.0)[torch.div(order, NU, rounding_mode="floor")]
+        counts = torch.bincount(sel_asc.reshape(-1).to(torch.int64), minlength=NE).to(torch.int32)
+        pair_index = torch.empty(order.numel(), dtype=torch.int32)
+        pair_index[order] = torch.arange(order.numel(), dtype=torch.int32)
+        return sel_asc, cw, rows, counts, pair_index
 
     def ep_experts(self, L, rows, offsets, flavour, row_index=None):
         out = torch.empty_like(rows)
@@ -46,7 +56,7 @@ class FakeStages:
         return out
 
     def ep_finish(self, L, x, pair_rows, pair_index=None):
-        sel_asc, cw, _ = self.ep_route(L, x, 0)
+        sel_asc, cw = self._route(L, x)
         M, NU = cw.shape
         pr = pair_rows.reshape(M * NU, -1)
         if pair_index is not None:
@@ -57,9 +67,9 @@ class FakeStages:
 def single_process(x, n_layers):
     f = FakeStages(CFG)
     for L in range(n_layers):
-        sel_asc, cw, rows = f.ep_route(L, x, 0)
+        sel_asc, cw = f._route(L, x)
         e = sel_asc.to(torch.float32).unsqueeze(-1)
-        pair = rows.unsqueeze(1) * (e + 1) + e
+        pair = (x * 2.0).unsqueeze(1) * (e + 1) + e
         x = x + (cw.unsqueeze(-1) * pair).sum(1)
     return x
 
@@ -108,6 +118,22 @@ def test_plan_dispatch_orders_pairs_by_owner():
     assert counts.tolist() == [4, 5]
     off = ep.expert_offsets(e, 8)
     assert off.tolist() == [0, 1, 2, 3, 4, 6, 7, 8, 9]
+
+
+def test_recv_layout_merges_source_blocks_by_expert():
+    # 2 ranks, 4 experts (2 each); rank 1 owns experts 2, 3
+    counts_all = torch.tensor([[1, 0, 2, 1], [3, 1, 0, 2]], dtype=torch.int32)
+    off, idx = ep.recv_layout(counts_all, 1, 5)
+    # arrival on rank 1: from rank 0: e2, e2, e3 (rows 0-2); from rank 1: e3, e3 (rows 3-4)
+    assert off.tolist() == [0, 0, 0, 2, 5]
+    assert idx.tolist() == [0, 1, 2, 3, 4]
+    off0, idx0 = ep.recv_layout(counts_all, 0, 5)
+    # arrival on rank 0: from rank 0: e0 (row 0); from rank 1: e0, e0, e0, e1 (rows 1-4) -> already sorted
+    assert off0.tolist() == [0, 4, 5, 5, 5] and idx0.tolist() == [0, 1, 2, 3, 4]
+    counts_all = torch.tensor([[1, 2, 0, 0], [1, 1, 0, 0]], dtype=torch.int32)
+    off, idx = ep.recv_layout(counts_all, 0, 5)
+    # arrival: r0: e0, e1, e1 (rows 0-2); r1: e0, e1 (rows 3-4) -> sorted: e0: rows 0, 3; e1: rows 1, 2, 4
+    assert off.tolist() == [0, 2, 5, 5, 5] and idx.tolist() == [0, 3, 1, 2, 4]
 
 
 def test_world_must_divide_experts():

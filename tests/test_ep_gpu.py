@@ -16,17 +16,13 @@ A, B = 0, 1
 
 def _chain_stages(eng, cfg, x, n_layers, flavour):
     import torch
-    from kairos_engine_b200 import ep
-    NE, NU, E = cfg["NE"], cfg["NU"], cfg["E"]
+    NE = cfg["NE"]
     for L in range(n_layers):
-        sel_asc, cw, rows = eng.ep_route(L, x, flavour)
-        order, _ = ep.plan_dispatch(sel_asc, NE, 1)
-        e_sorted = sel_asc.reshape(-1)[order]
-        rows_sorted = rows[torch.div(order, NU, rounding_mode="floor")].contiguous()
-        out_sorted = eng.ep_experts(L, rows_sorted, ep.expert_offsets(e_sorted, NE), flavour)
-        pair = torch.empty_like(out_sorted)
-        pair[order] = out_sorted
-        x = eng.ep_finish(L, x, pair.view(-1, NU, E))
+        sel_asc, cw, rows, counts, pair_index = eng.ep_route(L, x, flavour)
+        off = torch.zeros(NE + 1, dtype=torch.int32, device=x.device)
+        off[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        out = eng.ep_experts(L, rows, off, flavour)                  # the send buffer is already sorted by expert
+        x = eng.ep_finish(L, x, out, pair_index=pair_index)
     return x
 
 
