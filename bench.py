@@ -124,11 +124,8 @@ def cpu_time_tokens(layers, n_tokens, threads, seed=0):
 
 def run_reference(args, rank, world):
     import torch
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("gloo" if not torch.cuda.is_available() else "nccl")
-        if rank != 0:
-            dist.barrier(); dist.destroy_process_group(); return
+    if rank != 0:                                      # rank 0 alone runs the CPU arm; the others leave without work
+        return
     threads = min(os.cpu_count() or 1, 16)            # the reference pool's cap (moe_cpu_expert.c:225)
     layers = cpu_layers(4, torch)
     tok = 1                                            # one step = one token through 30 layers
@@ -144,8 +141,6 @@ def run_reference(args, rank, world):
             "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier(); dist.destroy_process_group()
 
 
 # ---------------------------------------------------------------- batched decode / draft-verify shapes
@@ -267,8 +262,9 @@ def run_ours(args, rank, local_rank, world):
     NL = args.layers
     PT = 0 if args.no_prefill else max(world, args.prefill_tokens // world * world)      # prefill tokens of the whole job
     eng = MoeEngine(n_layers=NL, max_tokens=max(1, PT // world), device=local_rank, max_expert_rows=PT * CFG["NU"] if world > 1 else 0, **CFG)
+    bias = synth.zipf_bias(CFG["NE"], s=args.zipf, seed=3, device=f"cuda:{local_rank}") if args.zipf > 0 else None
     for L in range(NL):
-        layer = synth.make_layer(CFG, 1000 * L, device=f"cuda:{local_rank}")
+        layer = synth.make_layer(CFG, 1000 * L, device=f"cuda:{local_rank}", bias=bias)
         eng.upload_layer(L, layer, on_device=True)
         del layer
     torch.cuda.empty_cache()
@@ -341,7 +337,7 @@ def run_ours(args, rank, local_rank, world):
                 "scaling": "weak", "vs_baseline": None, "dtype": "int8 activations x int4 weights, f32 accumulate", "data": "synthetic",
                 "config": {"workload": "configs[1]: 30-layer MoE FFN stack (Gemma-4-26B-A4B geometry), decode M=1, sequential tokens, "
                                        "all experts resident", "layers": NL, "tokens_per_step": T, "parallelism": "replicas" if world > 1 else "single GPU",
-                           "l2": "weights 13.2 GB per pass, far larger than L2: no flush needed"},
+                           "l2": "weights 13.2 GB per pass, far larger than L2: no flush needed", "router_bias": f"zipf s={args.zipf}" if args.zipf > 0 else "none"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                              "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if NL == N_LAYERS else None, "algorithmic_bytes_per_launch": bytes_per_launch, "kernel": "decode graph: per layer k_dg_router_shared + k_dg_experts_up + k_dg_experts_down (one graph launch = one token through the stack)",
                              "launch_ms": launch_ms},
@@ -380,6 +376,7 @@ def main():
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP, help="profiling aid: fewer sequential tokens per step than the workload's 256")
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill leg (whole job)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
+    ap.add_argument("--zipf", type=float, default=0.0, help="load-imbalance stress: add a Zipf(s) per-expert bias to every router (0 = unbiased)")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="profiling aid: a shorter stack than the workload's 30 layers (not a bench result)")
     args = ap.parse_args()
     rank, local_rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

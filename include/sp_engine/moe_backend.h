@@ -117,7 +117,9 @@ int  sp_moe_status(sp_moe *h);
  *             pair's input row - x normalised with pre_ffw_norm_2 - sorted by expert, so by owner:
  *             the all-to-all send buffer), counts[NE] (pairs per expert), pair_index[M*NU] (the row
  *             of pair t*NU+k in that buffer, and so in what comes back); sel/wts as in
- *             sp_moe_forward (or NULL)
+ *             sp_moe_forward (or NULL). defer_shared != 0 leaves the shared expert out: call
+ *             sp_moe_ep_shared_dev (same layer, flavour, M) any time before finish - typically right
+ *             after starting the dispatch exchange, so the two overlap
  *   experts : rows_in[n_rows][E] -> rows_out[n_rows][E] = down(geglu(gate|up(row))) with the weights of
  *             the row's expert. Sorted by expert, position p belongs to expert e when
  *             offsets[e] <= p < offsets[e+1] (offsets: NE+1 ints, device memory) and is row
@@ -128,7 +130,9 @@ int  sp_moe_status(sp_moe *h);
  * A run through the three stages is bit-identical to sp_moe_forward_dev on the same tokens. */
 int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,
                         int32_t *sel_asc_dev, float *cw_dev, float *rows_dev, int32_t *counts_dev,
-                        int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, void *stream);
+                        int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, int defer_shared,
+                        void *stream);
+int sp_moe_ep_shared_dev(sp_moe *h, int layer, int flavour, int M, void *stream);
 int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev,
                           const int32_t *row_index_dev, const int32_t *offsets_dev, float *rows_out_dev,
                           void *stream);

@@ -361,7 +361,8 @@ static int check_ep(sp_moe *h, int L, int flavour, const char *who) {
     return SP_MOE_OK;
 }
 extern "C" int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev, int32_t *sel_asc_dev, float *cw_dev,
-                                   float *rows_dev, int32_t *counts_dev, int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, void *stream) {
+                                   float *rows_dev, int32_t *counts_dev, int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, int defer_shared,
+                                   void *stream) {
     int rc = check_ep(h, layer, flavour, "sp_moe_ep_route_dev");
     if (rc) return rc;
     if (!x_dev || !sel_asc_dev || !cw_dev || !rows_dev || !counts_dev || !pair_index_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: NULL argument");
@@ -370,9 +371,20 @@ extern "C" int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, con
     cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
     int nlaunch = 0;
     cudaError_t e = sp_batched_ep_route(h->d, h->layers_host[layer], flavour, M, x_dev, sel_asc_dev, cw_dev, rows_dev, counts_dev, pair_index_dev, sel_dev, wts_dev,
-                                        &h->bs, h->status, st, &nlaunch);
+                                        defer_shared, &h->bs, h->status, st, &nlaunch);
     h->launches += (uint64_t)nlaunch;
     return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel route launch");
+}
+extern "C" int sp_moe_ep_shared_dev(sp_moe *h, int layer, int flavour, int M, void *stream) {
+    int rc = check_ep(h, layer, flavour, "sp_moe_ep_shared_dev");
+    if (rc) return rc;
+    if (M <= 0 || M > h->cfg.max_tokens) return fail(SP_MOE_EBADARG, "sp_moe_ep_shared_dev: M=%d outside (0, max_tokens=%d]", M, h->cfg.max_tokens);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_ep_shared(h->d, h->layers_host[layer], flavour, M, &h->bs, h->status, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel shared-expert launch");
 }
 extern "C" int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev, const int32_t *row_index_dev,
                                      const int32_t *offsets_dev, float *rows_out_dev, void *stream) {

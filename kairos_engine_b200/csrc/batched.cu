@@ -487,26 +487,11 @@ __global__ void __launch_bounds__(256) k_b_dispatch_rows(const float *in_f, cons
  *             those experts (any subset: empty groups cost nothing);
  *   finish  : ordered combine of the returned pair rows + the recombine.
  * The arithmetic of each pair is the single-GPU batched path's, so a split run is bit-identical. */
+/* the shared (always-on) expert of the tokens the last route call prepared: nx -> dn in the scratch */
 template <bool FA>
-cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows, int32_t *counts,
-                     int32_t *pair_index, int32_t *sel, float *wts, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
-    const int E = d.E, NE = d.NE, NU = d.NU, FFS = d.FFS;
-    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, FA ? v.in_f : nullptr); (*nl)++;
-    cudaError_t e = cudaSuccess;
-    k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
-    k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
-    /* the send buffer: rows sorted by expert (so also by owner), ready for the all-to-all */
-    k_b_scan<<<1, 1024, 0, st>>>(v.count, NE, v.ep_off); (*nl)++;
-    k_b_dispatch_rows<<<M * NU, 256, 0, st>>>(v.in_f, v.sel_asc, v.pairpos, v.ep_off, NU, E, rows, pair_index); (*nl)++;
-    e = cudaMemcpyAsync(counts, v.count, (size_t)4 * NE, cudaMemcpyDeviceToDevice, st);
-    if (e != cudaSuccess) return e;
-    if (!FA && tc) {
-        e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
-        if (e != cudaSuccess) return e;
-        e = cudaMemcpyAsync(sel_asc, v.sel_asc, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
-        if (e != cudaSuccess) return e;
-        return cudaMemcpyAsync(cw, v.cw, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
-    }
+cudaError_t ep_shared(const SpDims &d, const SpLayerDev &L, int M, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+    const int E = d.E, FFS = d.FFS;
+    if (!FA && tc) return sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
     GroupArgs g{};
     g.M = M;
     g.codes = L.sg_codes; g.bs = L.sg_bs; g.ucodes = L.su_codes; g.ubs = L.su_bs;
@@ -516,11 +501,28 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
     g.codes = L.sd_codes; g.bs = L.sd_bs; g.ucodes = nullptr; g.ubs = nullptr;
     g.in = FFS; g.rows = E; g.q = v.hd_q; g.sx = v.hd_s; g.corr = v.hd_c; g.xf = v.hd; g.out = v.dn; g.out_stride = E;
     launch_rows<FA, false>(g, 1, st, nl);
+    return cudaGetLastError();
+}
+
+template <bool FA>
+cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows, int32_t *counts,
+                     int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+    const int E = d.E, NE = d.NE, NU = d.NU;
+    k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, FA ? v.in_f : nullptr); (*nl)++;
+    cudaError_t e = cudaSuccess;
+    k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
+    k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
+    /* the send buffer: rows sorted by expert (so also by owner), ready for the all-to-all */
+    k_b_scan<<<1, 1024, 0, st>>>(v.count, NE, v.ep_off); (*nl)++;
+    k_b_dispatch_rows<<<M * NU, 256, 0, st>>>(v.in_f, v.sel_asc, v.pairpos, v.ep_off, NU, E, rows, pair_index); (*nl)++;
+    e = cudaMemcpyAsync(counts, v.count, (size_t)4 * NE, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return e;
     e = cudaMemcpyAsync(sel_asc, v.sel_asc, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return e;
     e = cudaMemcpyAsync(cw, v.cw, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return e;
-    return cudaGetLastError();
+    if (defer_shared) return cudaGetLastError();
+    return ep_shared<FA>(d, L, M, v, tc, status, st, nl);
 }
 
 template <bool FA>
@@ -545,12 +547,19 @@ cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float 
 }  // namespace
 
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
-                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, SpBatchedScratch *s, int *status,
+                                cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
     if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, v, s->tc, status, st, nlaunch)
-                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, v, s->tc, status, st, nlaunch)
+                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, v, s->tc, status, st, nlaunch);
+}
+cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+    *nlaunch = 0;
+    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
+    BView v = bview(d, s);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_shared<true>(d, L, M, v, s->tc, status, st, nlaunch) : ep_shared<false>(d, L, M, v, s->tc, status, st, nlaunch);
 }
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {

@@ -115,7 +115,7 @@ class MoeEngine:
         check(_lib.lib().sp_moe_status(self._h))
 
     # -- one layer in three stages (expert-parallel runs move rows between them; see ep.py)
-    def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None):
+    def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None, defer_shared=False):
         """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 [M*NU][E] sorted by
         expert, counts int32 [NE], pair_index int32 [M*NU])."""
         import torch
@@ -127,8 +127,14 @@ class MoeEngine:
         pair_index = torch.empty(M * NU, dtype=torch.int32, device=x.device)
         st = torch.cuda.current_stream(x.device).cuda_stream
         check(_lib.lib().sp_moe_ep_route_dev(self._h, layer, flavour, M, x.data_ptr(), sel_asc.data_ptr(), cw.data_ptr(),
-                                             rows.data_ptr(), counts.data_ptr(), pair_index.data_ptr(), _ptr(sel), _ptr(wts), st))
+                                             rows.data_ptr(), counts.data_ptr(), pair_index.data_ptr(), _ptr(sel), _ptr(wts),
+                                             1 if defer_shared else 0, st))
         return sel_asc, cw, rows, counts, pair_index
+
+    def ep_shared(self, layer, M, flavour=FLAVOUR_PREFILL):
+        """The shared expert of the tokens the last ep_route(defer_shared=True) call prepared."""
+        import torch
+        check(_lib.lib().sp_moe_ep_shared_dev(self._h, layer, flavour, M, torch.cuda.current_stream().cuda_stream))
 
     def ep_experts(self, layer, rows, offsets, flavour=FLAVOUR_PREFILL, row_index=None):
         """rows torch CUDA f32 [R][E], offsets int32 [NE+1]; sorted position p is row row_index[p]

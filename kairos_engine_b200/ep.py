@@ -77,7 +77,7 @@ class ExpertParallelMoe:
         NE, NU, E = self.cfg["NE"], self.cfg["NU"], self.cfg["E"]
         M, world, epr = x.shape[0], self.world, self.cfg["NE"] // self.world
         # route: the send buffer comes back already sorted by expert (= by owner)
-        sel_asc, cw, rows, counts, pair_index = self.engine.ep_route(L, x, flavour)
+        sel_asc, cw, rows, counts, pair_index = self.engine.ep_route(L, x, flavour, defer_shared=True)
         gathered = [torch.empty_like(counts) for _ in range(world)]
         dist.all_gather(gathered, counts, group=self.group)
         counts_all = torch.stack(gathered)                                   # [world][NE]
@@ -87,8 +87,10 @@ class ExpertParallelMoe:
         sc, rc = torch.stack([send_counts, recv_counts]).tolist()
         R = sum(rc)
         recv_rows = torch.empty((R, E), dtype=rows.dtype, device=x.device)
-        self._a2a(recv_rows, rows, rc, sc)
+        work = dist.all_to_all_single(recv_rows, rows, output_split_sizes=rc, input_split_sizes=sc, group=self.group, async_op=True)
+        self.engine.ep_shared(L, M, flavour)                                 # the shared expert runs under the dispatch
         offsets, row_index = recv_layout(counts_all, self.rank, R)
+        work.wait()
         self.last_rows = R
         out_recv = self.engine.ep_experts(L, recv_rows, offsets, flavour, row_index=row_index)
         back = torch.empty((M * NU, E), dtype=rows.dtype, device=x.device)

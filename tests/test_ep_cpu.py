@@ -31,7 +31,11 @@ class FakeStages:
         cw = torch.softmax(torch.gather(s, 1, sel_asc.to(torch.int64)), dim=1)
         return sel_asc, cw
 
-    def ep_route(self, L, x, flavour):
+    def ep_shared(self, L, M, flavour):
+        self.shared_calls = getattr(self, "shared_calls", 0) + 1
+
+    def ep_route(self, L, x, flavour, defer_shared=False):
+        assert defer_shared
         sel_asc, cw = self._route(L, x)
         NU, NE = self.cfg["NU"], self.cfg["NE"]
         order, _ = ep.plan_dispatch(sel_asc, NE, 1)

@@ -18,7 +18,9 @@ def _chain_stages(eng, cfg, x, n_layers, flavour):
     import torch
     NE = cfg["NE"]
     for L in range(n_layers):
-        sel_asc, cw, rows, counts, pair_index = eng.ep_route(L, x, flavour)
+        sel_asc, cw, rows, counts, pair_index = eng.ep_route(L, x, flavour, defer_shared=bool(L & 1))
+        if L & 1:
+            eng.ep_shared(L, x.shape[0], flavour)
         off = torch.zeros(NE + 1, dtype=torch.int32, device=x.device)
         off[1:] = torch.cumsum(counts, 0).to(torch.int32)
         out = eng.ep_experts(L, rows, off, flavour)                  # the send buffer is already sorted by expert
