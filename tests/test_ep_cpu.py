@@ -1,4 +1,4 @@
-"""Host logic of the expert-parallel run on CPU: two gloo ranks, a stand-in for the three stage
+"""Host logic of the expert-parallel run on CPU: 2, 4 and 8 gloo ranks, a stand-in for the stage
 calls whose arithmetic is simple enough to restate in one process."""
 import os
 import socket
@@ -98,9 +98,9 @@ def _rank_main(rank, world, port, tokens, n_layers, out_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("tokens", [(5, 9), (1, 16), (7, 7)])
-def test_two_ranks_match_single_process(tokens):
-    world, n_layers = 2, 3
+@pytest.mark.parametrize("tokens", [(5, 9), (1, 16), (7, 7), (3, 6, 2, 9), (4, 4, 4, 4, 1, 7, 2, 5)])
+def test_ranks_match_single_process(tokens):
+    world, n_layers = len(tokens), 3            # 2, 4 and 8 ranks over the 8 experts
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
