@@ -307,14 +307,15 @@ def run_ours(args, rank, local_rank, world):
 
     # ---- e2e: the host-pointer C-ABI call, pinned host buffers, copies inside the timed region
     xh = xs.cpu().pin_memory().numpy()
+    yh = torch.empty((1, E), dtype=torch.float32).pin_memory().numpy()      # page-locked result buffer, as a serving loop would hold
     e2e_steps = max(1, min(args.steps, 4))
     for t in range(min(8, T)):
-        eng.forward(xh[t:t + 1], want_routing=False)
+        eng.forward(xh[t:t + 1], want_routing=False, out=yh)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         for t in range(T):
-            eng.forward(xh[t:t + 1], want_routing=False)
+            eng.forward(xh[t:t + 1], want_routing=False, out=yh)
     barrier()
     e2e_s = time.perf_counter() - t0
     if dist is not None:

@@ -58,6 +58,7 @@ struct sp_moe {
     unsigned long long *xch;    /* exchange words: logits | hd | dn | h | acc */
     size_t xch_words;
     int *status;
+    int *status_host;           /* page-locked copy target: one synchronisation reads the error word */
     unsigned epoch;
     int dec_grid, dec_slots; size_t dec_smem;
     /* host-pointer entry staging */
@@ -153,6 +154,7 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     OPEN_CK(cudaMemset(h->xch, 0, 8 * h->xch_words), "memset");
     OPEN_CK(dalloc((void **)&h->status, 256), "scratch");
     OPEN_CK(cudaMemset(h->status, 0, 256), "memset");
+    OPEN_CK(cudaMallocHost((void **)&h->status_host, 64), "status word (host)");
     const size_t mt = (size_t)c.max_tokens;
     OPEN_CK(dalloc((void **)&h->x_dev, 4 * mt * c.E), "staging"); OPEN_CK(dalloc((void **)&h->y_dev, 4 * mt * c.E), "staging");
     OPEN_CK(dalloc((void **)&h->sel_dev, 4 * mt * c.NU * c.n_layers), "staging"); OPEN_CK(dalloc((void **)&h->wts_dev, 4 * mt * c.NU * c.n_layers), "staging");
@@ -205,6 +207,7 @@ extern "C" int sp_moe_close(sp_moe *h) {
     for (auto &g : h->bgraphs) if (g.exec) cudaGraphExecDestroy(g.exec);
     void *ps[] = {h->gs_base, h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
     for (void *p : ps) if (p) cudaFree(p);
+    if (h->status_host) cudaFreeHost(h->status_host);
     cudaGetLastError();
     delete h;
     return SP_MOE_OK;
@@ -419,9 +422,9 @@ extern "C" int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_
 extern "C" int sp_moe_status(sp_moe *h) {
     if (!h) return fail(SP_MOE_EBADARG, "sp_moe_status: NULL handle");
     CK(cudaSetDevice(h->device), "cudaSetDevice");
+    CK(cudaMemcpyAsync(h->status_host, h->status, sizeof(int), cudaMemcpyDeviceToHost, h->last_stream), "status D2H");
     CK(cudaStreamSynchronize(h->last_stream), "stream synchronize");
-    int st = 0;
-    CK(cudaMemcpy(&st, h->status, sizeof st, cudaMemcpyDeviceToHost), "status D2H");
+    const int st = *h->status_host;
     if (st == SP_KERR_NONE) return SP_MOE_OK;
     cudaMemset(h->status, 0, sizeof(int));
     if (st == SP_KERR_BARRIER_TIMEOUT) {

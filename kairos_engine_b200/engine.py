@@ -77,12 +77,15 @@ class MoeEngine:
         check(fn(self._h, layer, C.byref(w)))
 
     # -- forward
-    def forward(self, x, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, want_routing=True):
-        """Host entry: x numpy [M][E] f32 -> (y, sel, wts); sel/wts are [n_layers][M][NU]."""
+    def forward(self, x, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, want_routing=True, out=None):
+        """Host entry: x numpy [M][E] f32 -> (y, sel, wts); sel/wts are [n_layers][M][NU]. `out`: a caller-owned
+        [M][E] f32 array for y (page-locked memory makes the copy back asynchronous)."""
         n_layers = self.n_layers - layer_first if n_layers is None else n_layers
         x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.cfg["E"])
         M = x.shape[0]
-        y = np.empty_like(x)
+        y = np.empty_like(x) if out is None else out
+        if y.shape != x.shape or y.dtype != np.float32 or not y.flags["C_CONTIGUOUS"]:
+            raise ValueError("out must be a C-contiguous float32 array of x's shape")
         sel = np.empty((n_layers, M, self.cfg["NU"]), np.int32) if want_routing else None
         wts = np.empty((n_layers, M, self.cfg["NU"]), np.float32) if want_routing else None
         if self._trace.on and sel is None:           # the trace needs the routing even if the caller does not
