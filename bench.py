@@ -258,7 +258,8 @@ def run_ours(args, rank, local_rank, world):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=300))
     NL = args.layers
     PT = 0 if args.no_prefill else max(world, args.prefill_tokens // world * world)      # prefill tokens of the whole job
     eng = MoeEngine(n_layers=NL, max_tokens=max(1, PT // world), device=local_rank, max_expert_rows=PT * CFG["NU"] if world > 1 else 0, **CFG)
@@ -324,9 +325,15 @@ def run_ours(args, rank, local_rank, world):
         e2e_s = float(ts.item())
     e2e_v = T * e2e_steps * world / e2e_s
 
-    prefill = prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier) if PT else None
-    small = small_batch_leg(eng, NL, local_rank, rank) if (PT and world == 1) else None
-    igemm = int_gemm_leg(local_rank) if (PT and world == 1) else None
+    def extra(fn, *a):                                # the legs beside the headline must not take the headline down
+        try:
+            return fn(*a)
+        except Exception as e:  # reported in the line instead
+            return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    prefill = extra(prefill_leg, args, eng, NL, PT, rank, local_rank, world, dist, barrier) if PT else None
+    small = extra(small_batch_leg, eng, NL, local_rank, rank) if (PT and world == 1) else None
+    igemm = extra(int_gemm_leg, local_rank) if (PT and world == 1) else None
 
     if rank == 0:
         peak, peak_kind = measured_peak()
