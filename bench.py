@@ -200,11 +200,15 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     """PT tokens through the stack in the prefill arithmetic: one GPU runs them all; N GPUs run
     PT/N tokens each with the routed experts partitioned NE/N per GPU (all-to-all each way)."""
     import torch
-    from kairos_engine_b200 import FLAVOUR_PREFILL, ep, synth
+    from kairos_engine_b200 import FLAVOUR_PREFILL, SpMoeError, ep, synth
     Ml = PT // world
     xp = synth.make_inputs(CFG, Ml, seed=99 + rank, device=f"cuda:{local_rank}")
     yp = torch.empty_like(xp)
-    epm = ep.ExpertParallelMoe(eng, CFG) if world > 1 else None
+    # from four ranks on: padded exchange (no host read per layer) with room for twice the average rows per
+    # destination (at two ranks the doubled bytes cost more than the host read saves: 58.8 K vs 69.4 K tokens/s);
+    # the load-imbalance stress uses the exact exchange
+    cap = 0 if (world < 4 or args.zipf > 0) else -(-2 * Ml * CFG["NU"] // world // 8) * 8
+    epm = ep.ExpertParallelMoe(eng, CFG, capacity_rows=cap) if world > 1 else None
 
     def one_pass():
         if epm is None:
@@ -212,9 +216,26 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
         else:
             epm.forward(xp, 0, NL, FLAVOUR_PREFILL)
 
-    for _ in range(2):
-        one_pass()
-    eng.status()
+    def warm():
+        for _ in range(2):
+            one_pass()
+        try:
+            eng.status()
+            return 1
+        except SpMoeError:
+            return 0
+
+    ok = warm()
+    if dist is not None:
+        t = torch.tensor([ok], device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = int(t.item())
+    if not ok:
+        if epm is None or epm.capacity == 0:
+            raise RuntimeError("prefill warm-up reported a kernel error")
+        epm.capacity = cap = 0                         # some destination overflowed its block on some rank: all ranks go exact
+        if not warm():
+            raise RuntimeError("prefill warm-up reported a kernel error")
     barrier()
     passes = 3
     l0 = eng.kernel_launches
@@ -243,6 +264,7 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     return {"metric": "MoE-FFN prefill tokens/s (30-layer stack)", "value": PT * passes / (ms / 1e3), "unit": "tokens/s", "tokens": PT,
             "ms_per_pass": ms / passes, "passes": passes, "dtype": "f16 x f16 split operands (3 MMAs per k-step), f32 accumulate in TMEM",
             "parallelism": "single GPU" if world == 1 else f"expert-parallel: {PT // world} tokens and {CFG['NE'] // world} experts per GPU, all-to-all each way",
+            "exchange": "none" if world == 1 else (f"padded: {cap} rows per destination, no host read per layer" if cap else "exact: split sizes read on the host once per layer"),
             "expert_rows_last_layer": {"max_per_gpu": rows_max, "min_per_gpu": rows_min},
             "gpu_launches": int(eng.kernel_launches - l0),
             "tensor": {"algorithmic_tflops_per_gpu": tf, "peak": peak_tf, "frac": (tf / peak_tf) if peak_tf else None,

@@ -119,7 +119,13 @@ int  sp_moe_status(sp_moe *h);
  *             of pair t*NU+k in that buffer, and so in what comes back); sel/wts as in
  *             sp_moe_forward (or NULL). defer_shared != 0 leaves the shared expert out: call
  *             sp_moe_ep_shared_dev (same layer, flavour, M) any time before finish - typically right
- *             after starting the dispatch exchange, so the two overlap
+ *             after starting the dispatch exchange, so the two overlap. capacity > 0 (with n_ranks
+ *             ranks owning NE / n_ranks experts each) pads the buffer: rows for rank r start at row
+ *             r * capacity of rows[n_ranks * capacity][E], so the exchange needs no split sizes and
+ *             no host read; a rank's block that does not fit is reported by sp_moe_status
+ *   recv_layout (padded exchange only): counts_all[n_ranks][NE] (every rank's counts, gathered) ->
+ *             offsets[NE+1] and row_index[n_ranks * capacity] for the experts stage, whose n_rows
+ *             is then n_ranks * capacity
  *   experts : rows_in[n_rows][E] -> rows_out[n_rows][E] = down(geglu(gate|up(row))) with the weights of
  *             the row's expert. Sorted by expert, position p belongs to expert e when
  *             offsets[e] <= p < offsets[e+1] (offsets: NE+1 ints, device memory) and is row
@@ -131,7 +137,9 @@ int  sp_moe_status(sp_moe *h);
 int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev,
                         int32_t *sel_asc_dev, float *cw_dev, float *rows_dev, int32_t *counts_dev,
                         int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, int defer_shared,
-                        void *stream);
+                        int n_ranks, int capacity, void *stream);
+int sp_moe_ep_recv_layout_dev(sp_moe *h, const int32_t *counts_all_dev, int n_ranks, int rank, int capacity,
+                              int32_t *offsets_dev, int32_t *row_index_dev, void *stream);
 int sp_moe_ep_shared_dev(sp_moe *h, int layer, int flavour, int M, void *stream);
 int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const float *rows_in_dev,
                           const int32_t *row_index_dev, const int32_t *offsets_dev, float *rows_out_dev,

@@ -13,7 +13,7 @@ EXPORTS = ("sp_last_error", "sp_set_error", "sp_moe_open", "sp_moe_close", "sp_m
            "sp_moe_upload_layer_dev", "sp_moe_device_bytes", "sp_moe_forward", "sp_moe_forward_dev",
            "sp_moe_status", "gemma4_moe_ffn_q4b_cuda", "sp_moe_q4b_quantize_dev",
            "sp_moe_q4b_dequantize_dev", "sp_moe_gemv_q4b_dev", "sp_moe_gemv_q4b_static_dev", "sp_moe_gelu_mul_dev", "sp_moe_kernel_launches",
-           "sp_moe_ep_route_dev", "sp_moe_ep_shared_dev", "sp_moe_ep_experts_dev", "sp_moe_ep_finish_dev",
+           "sp_moe_ep_route_dev", "sp_moe_ep_recv_layout_dev", "sp_moe_ep_shared_dev", "sp_moe_ep_experts_dev", "sp_moe_ep_finish_dev",
            "sp_moe_ext_open", "sp_moe_ext_close", "sp_moe_ext_upload_experts", "sp_moe_ext_moe",
            "sp_frob_matmul_q8_dev", "sp_frob_matmul_q4_dev")
 
@@ -71,7 +71,8 @@ def lib():
         L.sp_moe_gemv_q4b_static_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.sp_moe_gelu_mul_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         L.sp_moe_kernel_launches.argtypes = [C.c_void_p]
-        L.sp_moe_ep_route_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 8 + [C.c_int, C.c_void_p]
+        L.sp_moe_ep_route_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 8 + [C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.sp_moe_ep_recv_layout_dev.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.sp_moe_ep_shared_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.sp_moe_ep_experts_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 5
         L.sp_moe_ep_finish_dev.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 5

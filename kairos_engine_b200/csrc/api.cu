@@ -365,18 +365,34 @@ static int check_ep(sp_moe *h, int L, int flavour, const char *who) {
 }
 extern "C" int sp_moe_ep_route_dev(sp_moe *h, int layer, int flavour, int M, const float *x_dev, int32_t *sel_asc_dev, float *cw_dev,
                                    float *rows_dev, int32_t *counts_dev, int32_t *pair_index_dev, int32_t *sel_dev, float *wts_dev, int defer_shared,
-                                   void *stream) {
+                                   int n_ranks, int capacity, void *stream) {
     int rc = check_ep(h, layer, flavour, "sp_moe_ep_route_dev");
     if (rc) return rc;
     if (!x_dev || !sel_asc_dev || !cw_dev || !rows_dev || !counts_dev || !pair_index_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: NULL argument");
     if (M <= 0 || M > h->cfg.max_tokens) return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: M=%d outside (0, max_tokens=%d]", M, h->cfg.max_tokens);
+    if (capacity < 0 || (capacity > 0 && (n_ranks <= 0 || h->cfg.NE % n_ranks)))
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_route_dev: a capacity needs n_ranks > 0 dividing NE=%d (got n_ranks=%d capacity=%d)", h->cfg.NE, n_ranks, capacity);
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
     int nlaunch = 0;
     cudaError_t e = sp_batched_ep_route(h->d, h->layers_host[layer], flavour, M, x_dev, sel_asc_dev, cw_dev, rows_dev, counts_dev, pair_index_dev, sel_dev, wts_dev,
-                                        defer_shared, &h->bs, h->status, st, &nlaunch);
+                                        defer_shared, n_ranks, capacity, &h->bs, h->status, st, &nlaunch);
     h->launches += (uint64_t)nlaunch;
     return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel route launch");
+}
+extern "C" int sp_moe_ep_recv_layout_dev(sp_moe *h, const int32_t *counts_all_dev, int n_ranks, int rank, int capacity,
+                                         int32_t *offsets_dev, int32_t *row_index_dev, void *stream) {
+    if (!h || !counts_all_dev || !offsets_dev || !row_index_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_recv_layout_dev: NULL argument");
+    if (n_ranks <= 0 || h->cfg.NE % n_ranks || rank < 0 || rank >= n_ranks || capacity <= 0)
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_recv_layout_dev: need 0 <= rank < n_ranks, n_ranks dividing NE=%d, capacity > 0", h->cfg.NE);
+    if ((long long)n_ranks * capacity > h->bs.max_rows)
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_recv_layout_dev: n_ranks * capacity = %lld exceeds max_expert_rows=%d", (long long)n_ranks * capacity, h->bs.max_rows);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    int nlaunch = 0;
+    cudaError_t e = sp_batched_ep_recv_layout(h->d, counts_all_dev, n_ranks, rank, capacity, offsets_dev, row_index_dev, st, &nlaunch);
+    h->launches += (uint64_t)nlaunch;
+    return e == cudaSuccess ? SP_MOE_OK : fail_cuda(e, "expert-parallel receive layout launch");
 }
 extern "C" int sp_moe_ep_shared_dev(sp_moe *h, int layer, int flavour, int M, void *stream) {
     int rc = check_ep(h, layer, flavour, "sp_moe_ep_shared_dev");

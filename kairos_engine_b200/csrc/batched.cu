@@ -468,15 +468,61 @@ __global__ void __launch_bounds__(1024) k_b_scan(const int *count, int n, int *o
     if (t < n) off[t + 1] = sh[t];
     if (t == 0) off[0] = 0;
 }
-/* one block per (token, expert) pair: its input row goes to position off[e] + pairpos of the send buffer */
+/* one block per (token, expert) pair: its input row goes to position off[e] + pairpos of the send buffer.
+ * With a capacity (rows per destination rank, experts owned in blocks of epr) the buffer is padded: the rows
+ * for rank r start at r * capacity, so the exchange needs no split sizes; a block that would not fit is
+ * reported through the error word. */
 __global__ void __launch_bounds__(256) k_b_dispatch_rows(const float *in_f, const int *sel_asc, const int *pairpos, const int *off, int NU, int E,
-                                                         float *rows, int *pair_index) {
+                                                         int epr, int capacity, float *rows, int *pair_index, int *status) {
     const int p = blockIdx.x;
-    const int pos = off[sel_asc[p]] + pairpos[p];
+    const int e = sel_asc[p];
+    int pos = off[e] + pairpos[p];
+    if (capacity > 0) {
+        const int owner = e / epr, in_block = pos - off[owner * epr];
+        if (in_block >= capacity) {
+            if (threadIdx.x == 0) { pair_index[p] = owner * capacity; atomicExch(status, SP_KERR_OVERFLOW); }
+            return;
+        }
+        pos = owner * capacity + in_block;
+    }
     if (threadIdx.x == 0) pair_index[p] = pos;
     const float4 *src = reinterpret_cast<const float4 *>(in_f + (size_t)(p / NU) * E);
     float4 *dst = reinterpret_cast<float4 *>(rows + (size_t)pos * E);
     for (int i = threadIdx.x; i < E / 4; i += 256) dst[i] = src[i];
+}
+/* what a rank received through the padded exchange: source s's block starts at row s * capacity and holds
+ * its rows for this rank's experts, sorted by expert. counts_all[s][e] = pairs of expert e on rank s.
+ * Writes offsets[NE+1] (sorted position range of every expert; empty outside this rank's experts) and
+ * row_index[n_ranks * capacity] (sorted position -> arrival row; 0 beyond the rows that exist). */
+__global__ void __launch_bounds__(256) k_b_recv_layout(const int *counts_all, int NE, int n_ranks, int rank, int capacity, int *offsets, int *row_index) {
+    extern __shared__ int lsm[];                 /* cnt[nb], sorted_start[nb + 1], arrival_start[nb], all in (expert, source) order */
+    const int epr = NE / n_ranks, nb = epr * n_ranks, e0 = rank * epr;
+    int *cnt = lsm, *sorted_start = lsm + nb, *arrival_start = lsm + 2 * nb + 1;
+    for (int b = threadIdx.x; b < nb; b += 256) cnt[b] = counts_all[(b % n_ranks) * NE + e0 + b / n_ranks];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int b = 0; b < nb; b++) { sorted_start[b] = acc; acc += cnt[b]; }
+        sorted_start[nb] = acc;
+    }
+    if (threadIdx.x >= 32 && threadIdx.x < 32 + n_ranks) {
+        const int s_ = threadIdx.x - 32;
+        int a = s_ * capacity;
+        for (int e = 0; e < epr; e++) { arrival_start[e * n_ranks + s_] = a; a += cnt[e * n_ranks + s_]; }
+    }
+    __syncthreads();
+    const int total = sorted_start[nb];
+    for (int e = threadIdx.x; e <= NE; e += 256)
+        offsets[e] = e < e0 ? 0 : (e >= e0 + epr ? total : sorted_start[(e - e0) * n_ranks]);
+    for (int p = threadIdx.x; p < n_ranks * capacity; p += 256) {
+        int v = 0;
+        if (p < total) {
+            int lo = 0, hi = nb - 1;               /* the block that holds sorted position p */
+            while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (sorted_start[mid] <= p) lo = mid; else hi = mid - 1; }
+            v = arrival_start[lo] + (p - sorted_start[lo]);
+        }
+        row_index[p] = v;
+    }
 }
 
 /* ---------------------------------------------------------------- expert-parallel stages
@@ -506,7 +552,8 @@ cudaError_t ep_shared(const SpDims &d, const SpLayerDev &L, int M, BView &v, SpT
 
 template <bool FA>
 cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x, int32_t *sel_asc, float *cw, float *rows, int32_t *counts,
-                     int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+                     int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, int n_ranks, int capacity, BView &v, SpTcPlan *tc, int *status,
+                     cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, NU = d.NU;
     k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, FA ? v.in_f : nullptr); (*nl)++;
     cudaError_t e = cudaSuccess;
@@ -514,7 +561,7 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
     /* the send buffer: rows sorted by expert (so also by owner), ready for the all-to-all */
     k_b_scan<<<1, 1024, 0, st>>>(v.count, NE, v.ep_off); (*nl)++;
-    k_b_dispatch_rows<<<M * NU, 256, 0, st>>>(v.in_f, v.sel_asc, v.pairpos, v.ep_off, NU, E, rows, pair_index); (*nl)++;
+    k_b_dispatch_rows<<<M * NU, 256, 0, st>>>(v.in_f, v.sel_asc, v.pairpos, v.ep_off, NU, E, capacity > 0 ? NE / n_ranks : NE, capacity, rows, pair_index, status); (*nl)++;
     e = cudaMemcpyAsync(counts, v.count, (size_t)4 * NE, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return e;
     e = cudaMemcpyAsync(sel_asc, v.sel_asc, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
@@ -547,13 +594,20 @@ cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float 
 }  // namespace
 
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
-                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, SpBatchedScratch *s, int *status,
-                                cudaStream_t st, int *nlaunch) {
+                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, int n_ranks, int capacity,
+                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;
     if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, v, s->tc, status, st, nlaunch)
-                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, n_ranks, capacity, v, s->tc, status, st, nlaunch)
+                                            : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, n_ranks, capacity, v, s->tc, status, st, nlaunch);
+}
+cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all, int n_ranks, int rank, int capacity, int32_t *offsets, int32_t *row_index,
+                                      cudaStream_t st, int *nlaunch) {
+    *nlaunch = 1;
+    const int nb = d.NE;                                    /* epr * n_ranks */
+    k_b_recv_layout<<<1, 256, (size_t)(3 * nb + 1) * sizeof(int), st>>>(counts_all, d.NE, n_ranks, rank, capacity, offsets, row_index);
+    return cudaGetLastError();
 }
 cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
     *nlaunch = 0;

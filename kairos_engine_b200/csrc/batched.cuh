@@ -28,8 +28,11 @@ cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, i
  *             row_index[p] of rows_in and of rows_out (NULL = the rows are already sorted); R <= max_rows
  *   finish  : output of token t's k-th expert (ascending id) = pair_rows[pair_index[t*NU+k]] (NULL = t*NU+k) */
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
-                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, SpBatchedScratch *s, int *status,
-                                cudaStream_t st, int *nlaunch);
+                                float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, int n_ranks, int capacity,
+                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+/* receive side of the padded exchange (route called with a capacity): offsets[NE+1] and row_index[n_ranks*capacity] */
+cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all, int n_ranks, int rank, int capacity, int32_t *offsets, int32_t *row_index,
+                                      cudaStream_t st, int *nlaunch);
 /* the shared expert of the tokens the last route call prepared, when that call deferred it */
 cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,

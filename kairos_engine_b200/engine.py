@@ -118,21 +118,33 @@ class MoeEngine:
         check(_lib.lib().sp_moe_status(self._h))
 
     # -- one layer in three stages (expert-parallel runs move rows between them; see ep.py)
-    def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None, defer_shared=False):
-        """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 [M*NU][E] sorted by
-        expert, counts int32 [NE], pair_index int32 [M*NU])."""
+    def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None, defer_shared=False, n_ranks=0, capacity=0):
+        """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 sorted by expert,
+        counts int32 [NE], pair_index int32 [M*NU]). rows is [M*NU][E], or with a capacity the padded send
+        buffer [n_ranks*capacity][E] (rank r's rows start at r*capacity; unused rows are not initialised)."""
         import torch
         M, NU, NE = x.shape[0], self.cfg["NU"], self.cfg["NE"]
         sel_asc = torch.empty((M, NU), dtype=torch.int32, device=x.device)
         cw = torch.empty((M, NU), dtype=torch.float32, device=x.device)
-        rows = torch.empty((M * NU, x.shape[1]), dtype=torch.float32, device=x.device)
+        rows = torch.empty((n_ranks * capacity if capacity else M * NU, x.shape[1]), dtype=torch.float32, device=x.device)
         counts = torch.empty(NE, dtype=torch.int32, device=x.device)
         pair_index = torch.empty(M * NU, dtype=torch.int32, device=x.device)
         st = torch.cuda.current_stream(x.device).cuda_stream
         check(_lib.lib().sp_moe_ep_route_dev(self._h, layer, flavour, M, x.data_ptr(), sel_asc.data_ptr(), cw.data_ptr(),
                                              rows.data_ptr(), counts.data_ptr(), pair_index.data_ptr(), _ptr(sel), _ptr(wts),
-                                             1 if defer_shared else 0, st))
+                                             1 if defer_shared else 0, n_ranks, capacity, st))
         return sel_asc, cw, rows, counts, pair_index
+
+    def ep_recv_layout(self, counts_all, rank, capacity):
+        """counts_all torch CUDA int32 [n_ranks][NE] -> (offsets int32 [NE+1], row_index int32 [n_ranks*capacity])
+        for the rows a padded exchange delivered to `rank`."""
+        import torch
+        n_ranks = counts_all.shape[0]
+        offsets = torch.empty(self.cfg["NE"] + 1, dtype=torch.int32, device=counts_all.device)
+        row_index = torch.empty(n_ranks * capacity, dtype=torch.int32, device=counts_all.device)
+        check(_lib.lib().sp_moe_ep_recv_layout_dev(self._h, counts_all.contiguous().data_ptr(), n_ranks, rank, capacity, offsets.data_ptr(),
+                                                   row_index.data_ptr(), torch.cuda.current_stream(counts_all.device).cuda_stream))
+        return offsets, row_index
 
     def ep_shared(self, layer, M, flavour=FLAVOUR_PREFILL):
         """The shared expert of the tokens the last ep_route(defer_shared=True) call prepared."""

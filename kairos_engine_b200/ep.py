@@ -62,8 +62,13 @@ class ExpertParallelMoe:
     """engine: an object with ep_route / ep_experts / ep_finish (kairos_engine_b200.MoeEngine);
     cfg: its geometry dict. group: a torch.distributed process group (None = the default)."""
 
-    def __init__(self, engine, cfg, group=None):
+    def __init__(self, engine, cfg, group=None, capacity_rows=0):
+        """capacity_rows > 0: padded exchange - every rank sends exactly capacity_rows rows to every rank (the
+        same number on all ranks), so a layer needs no host read and the CPU can enqueue the whole stack ahead of
+        the GPU; a destination that would get more rows than that from one rank is reported by the engine's
+        status(). 0: exact exchange with split sizes read on the host once per layer."""
         self.engine, self.cfg, self.group = engine, cfg, group
+        self.capacity = int(capacity_rows)
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if cfg["NE"] % self.world:
@@ -73,7 +78,26 @@ class ExpertParallelMoe:
     def _a2a(self, out, inp, out_splits, in_splits):
         dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits, group=self.group)
 
+    def _layer_padded(self, L, x, flavour):
+        NU, E, world, C = self.cfg["NU"], self.cfg["E"], self.world, self.capacity
+        sel_asc, cw, rows, counts, pair_index = self.engine.ep_route(L, x, flavour, defer_shared=True, n_ranks=world, capacity=C)
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts, group=self.group)
+        counts_all = torch.stack(gathered)
+        recv_rows = torch.empty_like(rows)
+        work = dist.all_to_all_single(recv_rows, rows, group=self.group, async_op=True)      # equal splits: no sizes needed
+        self.engine.ep_shared(L, x.shape[0], flavour)
+        offsets, row_index = self.engine.ep_recv_layout(counts_all, self.rank, C)
+        work.wait()
+        self.last_rows = world * C
+        out_recv = self.engine.ep_experts(L, recv_rows, offsets, flavour, row_index=row_index)
+        back = torch.empty_like(rows)
+        dist.all_to_all_single(back, out_recv, group=self.group)
+        return self.engine.ep_finish(L, x, back, pair_index=pair_index)
+
     def layer(self, L, x, flavour):
+        if self.capacity > 0:
+            return self._layer_padded(L, x, flavour)
         NE, NU, E = self.cfg["NE"], self.cfg["NU"], self.cfg["E"]
         M, world, epr = x.shape[0], self.world, self.cfg["NE"] // self.world
         # route: the send buffer comes back already sorted by expert (= by owner)

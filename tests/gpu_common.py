@@ -9,11 +9,11 @@ MAX_ABS = 2e-3
 REL_L2 = 1e-3
 
 
-def make_stack(cfg, n_layers, seed=0, rand_norms=False, max_tokens=1, bias=None):
+def make_stack(cfg, n_layers, seed=0, rand_norms=False, max_tokens=1, bias=None, **engine_kw):
     """-> (engine, [orc.LayerWeights per layer]) holding identical bytes."""
     import torch
     from kairos_engine_b200 import MoeEngine, synth
-    eng = MoeEngine(n_layers=n_layers, max_tokens=max_tokens, **cfg)
+    eng = MoeEngine(n_layers=n_layers, max_tokens=max_tokens, **engine_kw, **cfg)
     host_layers = []
     for L in range(n_layers):
         layer = synth.make_layer(cfg, seed + 1000 * L, rand_norms=rand_norms, bias=bias)

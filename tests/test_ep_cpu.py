@@ -34,7 +34,7 @@ class FakeStages:
     def ep_shared(self, L, M, flavour):
         self.shared_calls = getattr(self, "shared_calls", 0) + 1
 
-    def ep_route(self, L, x, flavour, defer_shared=False):
+    def ep_route(self, L, x, flavour, defer_shared=False, n_ranks=0, capacity=0):
         assert defer_shared
         sel_asc, cw = self._route(L, x)
         NU, NE = self.cfg["NU"], self.cfg["NE"]
@@ -43,12 +43,38 @@ class FakeStages:
         counts = torch.bincount(sel_asc.reshape(-1).to(torch.int64), minlength=NE).to(torch.int32)
         pair_index = torch.empty(order.numel(), dtype=torch.int32)
         pair_index[order] = torch.arange(order.numel(), dtype=torch.int32)
+        if capacity:                                    # padded send buffer: rank r's rows start at r * capacity
+            epr = NE // n_ranks
+            per_rank = counts.view(n_ranks, epr).sum(1)
+            assert int(per_rank.max()) <= capacity, "test capacity too small"
+            start = torch.cumsum(per_rank, 0) - per_rank
+            e_sorted = sel_asc.reshape(-1)[order].to(torch.int64)
+            owner = e_sorted // epr
+            padded_pos = owner * capacity + (torch.arange(order.numel()) - start[owner])
+            padded = torch.full((n_ranks * capacity, x.shape[1]), float("nan"))
+            padded[padded_pos] = rows
+            pair_index = padded_pos[pair_index.to(torch.int64)].to(torch.int32)
+            rows = padded
         return sel_asc, cw, rows, counts, pair_index
+
+    def ep_recv_layout(self, counts_all, rank, capacity):
+        world, NE = counts_all.shape
+        epr = NE // world
+        c = counts_all[:, rank * epr:(rank + 1) * epr].to(torch.int64)
+        total = int(c.sum())
+        off, idx = ep.recv_layout(counts_all, rank, total)          # dense arrival numbering ...
+        arr = c.reshape(-1); dense_start = (torch.cumsum(arr, 0) - arr).view(world, epr)[:, 0]
+        src = torch.bucketize(idx.to(torch.int64), dense_start, right=True) - 1
+        padded = (idx.to(torch.int64) - dense_start[src] + src * capacity).to(torch.int32)   # ... moved to the padded blocks
+        out = torch.zeros(world * capacity, dtype=torch.int32)
+        out[:total] = padded
+        off = off.clone(); off[(rank + 1) * epr + 1:] = total
+        return off, out
 
     def ep_experts(self, L, rows, offsets, flavour, row_index=None):
         out = torch.empty_like(rows)
         off = offsets.tolist()
-        assert off[0] == 0 and off[-1] == rows.shape[0]
+        assert off[0] == 0 and off[-1] <= rows.shape[0]
         idx = torch.arange(rows.shape[0]) if row_index is None else row_index.to(torch.int64)
         for e in range(self.cfg["NE"]):
             if off[e + 1] > off[e]:
@@ -62,7 +88,7 @@ class FakeStages:
     def ep_finish(self, L, x, pair_rows, pair_index=None):
         sel_asc, cw = self._route(L, x)
         M, NU = cw.shape
-        pr = pair_rows.reshape(M * NU, -1)
+        pr = pair_rows.reshape(pair_rows.shape[0] if pair_index is not None else M * NU, -1)
         if pair_index is not None:
             pr = pr[pair_index.to(torch.int64)]
         return x + (cw.unsqueeze(-1) * pr.view(M, NU, -1)).sum(1)
@@ -83,7 +109,7 @@ def _free_port():
     return p
 
 
-def _rank_main(rank, world, port, tokens, n_layers, out_q):
+def _rank_main(rank, world, port, tokens, n_layers, out_q, capacity=0):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -91,7 +117,7 @@ def _rank_main(rank, world, port, tokens, n_layers, out_q):
         x = torch.randn(tokens[rank], CFG["E"], generator=g)
         per = CFG["NE"] // world
         eng = FakeStages(CFG, owned=set(range(rank * per, (rank + 1) * per)))
-        run = ep.ExpertParallelMoe(eng, CFG)
+        run = ep.ExpertParallelMoe(eng, CFG, capacity_rows=capacity)
         y = run.forward(x, 0, n_layers, 0)
         out_q.put((rank, x.numpy(), y.numpy(), sorted(set(eng.seen))))
     finally:
@@ -112,6 +138,22 @@ def test_ranks_match_single_process(tokens):
     for rank, x, y, seen in got:
         want = single_process(torch.from_numpy(x), n_layers).numpy()
         np.testing.assert_array_equal(y, want)
+
+
+@pytest.mark.parametrize("tokens", [(6, 6), (5, 5, 5, 5)])
+def test_padded_exchange_matches_single_process(tokens):
+    world, n_layers = len(tokens), 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    cap = tokens[0] * CFG["NU"]                      # worst case: every pair of a rank goes to one rank
+    ps = [ctx.Process(target=_rank_main, args=(r, world, port, tokens, n_layers, q, cap)) for r in range(world)]
+    for p in ps: p.start()
+    got = [q.get(timeout=120) for _ in ps]
+    for p in ps:
+        p.join(60); assert p.exitcode == 0
+    for rank, x, y, seen in got:
+        np.testing.assert_array_equal(y, single_process(torch.from_numpy(x), n_layers).numpy())
 
 
 def test_plan_dispatch_orders_pairs_by_owner():

@@ -79,12 +79,68 @@ def test_experts_stage_with_row_index_equals_sorted_rows(flavour):
     eng.close()
 
 
+@pytest.mark.parametrize("flavour", [A, B])
+def test_padded_route_and_receive_layout_equal_one_call(flavour):
+    import torch
+    cfg, M = orc.SMALL, 20
+    eng, _ = make_stack(cfg, 1, seed=34, rand_norms=True, max_tokens=M, max_expert_rows=M * orc.SMALL["NU"] + 16)
+    x = torch.from_numpy(np.random.default_rng(8).standard_normal((M, cfg["E"])).astype(np.float32)).cuda()
+    y = torch.empty_like(x)
+    eng.forward_dev(x, y, 0, 1, flavour)
+    C = M * cfg["NU"] + 16                                           # one "rank", padded beyond what exists
+    sel_asc, cw, rows, counts, pair_index = eng.ep_route(0, x, flavour, n_ranks=1, capacity=C)
+    assert rows.shape[0] == C
+    off, row_index = eng.ep_recv_layout(counts.view(1, -1), 0, C)
+    assert off.tolist() == [0] + torch.cumsum(counts, 0).tolist()
+    assert row_index[:M * cfg["NU"]].tolist() == list(range(M * cfg["NU"])) and int(row_index[M * cfg["NU"]:].abs().sum()) == 0
+    rows[M * cfg["NU"]:] = float("nan")                              # the padding must never be read into a result
+    out = eng.ep_experts(0, rows, off, flavour, row_index=row_index)
+    y2 = eng.ep_finish(0, x, out, pair_index=pair_index)
+    eng.status()
+    assert torch.equal(y.view(torch.int32), y2.view(torch.int32))
+    eng.close()
+
+
+def test_receive_layout_kernel_matches_host_arithmetic():
+    import torch
+    from kairos_engine_b200 import ep
+    cfg = orc.SMALL                                                  # 16 experts
+    eng, _ = make_stack(cfg, 1, seed=35, max_tokens=64)             # 256 expert rows: room for 4 x 40
+    world, C = 4, 40
+    g = torch.Generator().manual_seed(3)
+    counts_all = torch.randint(0, 10, (world, cfg["NE"]), generator=g, dtype=torch.int32)
+    epr = cfg["NE"] // world
+    for rank in range(world):
+        c = counts_all[:, rank * epr:(rank + 1) * epr].to(torch.int64)
+        total = int(c.sum())
+        off, idx = eng.ep_recv_layout(counts_all.cuda(), rank, C)
+        roff, ridx = ep.recv_layout(counts_all, rank, total)         # dense arrival numbering
+        dense_start = (torch.cumsum(c.sum(1), 0) - c.sum(1))
+        src = torch.bucketize(ridx.to(torch.int64), dense_start, right=True) - 1
+        want = ridx.to(torch.int64) - dense_start[src] + src * C      # the same rows in the padded blocks
+        assert off.cpu().tolist() == roff.tolist()
+        assert idx.cpu()[:total].tolist() == want.tolist() and int(idx.cpu()[total:].abs().sum()) == 0
+    eng.close()
+
+
+def test_padded_route_reports_a_block_that_does_not_fit():
+    import torch
+    from kairos_engine_b200 import SpMoeError
+    cfg, M = orc.SMALL, 16
+    eng, _ = make_stack(cfg, 1, seed=36, max_tokens=M)
+    x = torch.randn(M, cfg["E"], device="cuda")
+    eng.ep_route(0, x, B, n_ranks=2, capacity=8)                     # 64 pairs over two ranks cannot fit 8 rows each
+    with pytest.raises(SpMoeError):
+        eng.status()
+    eng.close()
+
+
 def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close()
     return p
 
 
-def _nccl_rank(rank, world, port, flavour, q):
+def _nccl_rank(rank, world, port, flavour, q, capacity=0):
     import torch
     import torch.distributed as dist
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -94,13 +150,13 @@ def _nccl_rank(rank, world, port, flavour, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         cfg, n_layers, M = orc.SMALL, 2, 24 + 8 * rank
-        eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, **cfg)
+        eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, max_expert_rows=max(256, 2 * capacity), **cfg)
         for L in range(n_layers):
             eng.upload_layer(L, synth.make_layer(cfg, 77 + 1000 * L, rand_norms=True, device=f"cuda:{rank}"), on_device=True)
         x = torch.from_numpy(np.random.default_rng(rank).standard_normal((M, cfg["E"])).astype(np.float32)).cuda()
         want = torch.empty_like(x)
         eng.forward_dev(x, want, 0, n_layers, flavour)
-        got = ep.ExpertParallelMoe(eng, cfg).forward(x, 0, n_layers, flavour)
+        got = ep.ExpertParallelMoe(eng, cfg, capacity_rows=capacity).forward(x, 0, n_layers, flavour)
         eng.status()
         torch.cuda.synchronize()
         q.put((rank, bool(torch.equal(got.view(torch.int32), want.view(torch.int32)))))
@@ -109,8 +165,8 @@ def _nccl_rank(rank, world, port, flavour, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("flavour", [A, B])
-def test_two_gpus_nccl_equal_single_gpu(flavour):
+@pytest.mark.parametrize("flavour,capacity", [(A, 0), (B, 0), (A, 160), (B, 160)])
+def test_two_gpus_nccl_equal_single_gpu(flavour, capacity):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -118,7 +174,7 @@ def test_two_gpus_nccl_equal_single_gpu(flavour):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, flavour, q)) for r in range(2)]
+    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, flavour, q, capacity)) for r in range(2)]
     for p in ps: p.start()
     got = [q.get(timeout=300) for _ in ps]
     for p in ps:
