@@ -204,10 +204,10 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     Ml = PT // world
     xp = synth.make_inputs(CFG, Ml, seed=99 + rank, device=f"cuda:{local_rank}")
     yp = torch.empty_like(xp)
-    # from four ranks on: padded exchange (no host read per layer) with room for twice the average rows per
-    # destination (at two ranks the doubled bytes cost more than the host read saves: 58.8 K vs 69.4 K tokens/s);
+    # from four ranks on: padded exchange (no host read per layer) with room for 1.25x the average rows per
+    # destination (unbiased routing spreads within a few percent; an overflow on any rank sends all ranks to the exact exchange) (at two ranks the doubled bytes cost more than the host read saves: 58.8 K vs 69.4 K tokens/s);
     # the load-imbalance stress uses the exact exchange
-    cap = 0 if (world < 4 or args.zipf > 0) else -(-2 * Ml * CFG["NU"] // world // 8) * 8
+    cap = 0 if (world < 4 or args.zipf > 0) else -(-5 * Ml * CFG["NU"] // (4 * world) // 8) * 8
     epm = ep.ExpertParallelMoe(eng, CFG, capacity_rows=cap) if world > 1 else None
 
     def one_pass():
@@ -239,10 +239,27 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     barrier()
     passes = 3
     l0 = eng.kernel_launches
+    one_pass()
+    per_pass_launches = eng.kernel_launches - l0
+    run, replayed = one_pass, False
+    if epm is not None and epm.capacity > 0 and not args.no_ep_graph:
+        # the padded exchange has no host read, so a whole pass (kernels + collectives) can be replayed from one
+        # CUDA graph and the CPU stops pacing the ranks
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                epm.forward(xp, 0, NL, FLAVOUR_PREFILL)
+            graph.replay()
+            torch.cuda.synchronize()
+            run, replayed = graph.replay, True
+        except Exception as e:
+            raise RuntimeError(f"CUDA-graph capture of the expert-parallel pass failed ({type(e).__name__}: {e}); rerun with --no-ep-graph")
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(passes):
-        one_pass()
+        run()
     e1.record()
     barrier()
     eng.status()
@@ -266,7 +283,7 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
             "parallelism": "single GPU" if world == 1 else f"expert-parallel: {PT // world} tokens and {CFG['NE'] // world} experts per GPU, all-to-all each way",
             "exchange": "none" if world == 1 else (f"padded: {cap} rows per destination, no host read per layer" if cap else "exact: split sizes read on the host once per layer"),
             "expert_rows_last_layer": {"max_per_gpu": rows_max, "min_per_gpu": rows_min},
-            "gpu_launches": int(eng.kernel_launches - l0),
+            "gpu_launches": int(per_pass_launches * passes), "replayed_from_cuda_graph": replayed,
             "tensor": {"algorithmic_tflops_per_gpu": tf, "peak": peak_tf, "frac": (tf / peak_tf) if peak_tf else None,
                        "note": "algorithmic FLOPs (2*M*N*K once) over the whole pass, all kernels included; the MMAs issued are 3x that"}}
 
@@ -406,6 +423,7 @@ def main():
     ap.add_argument("--tokens-per-step", type=int, default=TOKENS_PER_STEP, help="profiling aid: fewer sequential tokens per step than the workload's 256")
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill leg (whole job)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
+    ap.add_argument("--no-ep-graph", action="store_true", help="run the expert-parallel prefill pass eagerly instead of from a CUDA graph")
     ap.add_argument("--zipf", type=float, default=0.0, help="load-imbalance stress: add a Zipf(s) per-expert bias to every router (0 = unbiased)")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="profiling aid: a shorter stack than the workload's 30 layers (not a bench result)")
     args = ap.parse_args()
