@@ -204,10 +204,10 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier):
     Ml = PT // world
     xp = synth.make_inputs(CFG, Ml, seed=99 + rank, device=f"cuda:{local_rank}")
     yp = torch.empty_like(xp)
-    # from four ranks on: padded exchange (no host read per layer) with room for 1.25x the average rows per
-    # destination (unbiased routing spreads within a few percent; an overflow on any rank sends all ranks to the exact exchange) (at two ranks the doubled bytes cost more than the host read saves: 58.8 K vs 69.4 K tokens/s);
-    # the load-imbalance stress uses the exact exchange
-    cap = 0 if (world < 4 or args.zipf > 0) else -(-5 * Ml * CFG["NU"] // (4 * world) // 8) * 8
+    # N > 1: padded exchange (no host read per layer) with room for 1.25x the average rows per destination
+    # (unbiased routing spreads within a few percent; an overflow on any rank sends all ranks to the exact
+    # exchange); the load-imbalance stress uses the exact exchange
+    cap = 0 if (world < 2 or args.zipf > 0) else -(-5 * Ml * CFG["NU"] // (4 * world) // 8) * 8
     epm = ep.ExpertParallelMoe(eng, CFG, capacity_rows=cap) if world > 1 else None
 
     def one_pass():
