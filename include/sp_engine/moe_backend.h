@@ -226,6 +226,32 @@ int sp_moe_gelu_mul_dev(const float *g_dev, const float *up_dev, int64_t n, floa
  * CF:9020-9044): kernels launched by this handle since open. */
 uint64_t sp_moe_kernel_launches(const sp_moe *h);
 
+/* Phase timing of the single-token decode path: the counterpart of the reference's `[g4-moe] TIMING`
+ * accounting (CF:7186-7201, 9020-9044; switched on the same way, SP_MOE_TIMING=1 in the environment
+ * when the handle is opened - without it no clock is read and this call returns SP_MOE_EBADSTATE).
+ * The reference splits host wall time into sync / route / expert loop / stage; none of those exist
+ * here (no host round trip, nothing staged), so the phases are this path's own: for each of the
+ * three kernels of a layer, microseconds on the device clock between entry, the predecessor's
+ * results being visible, the end of the per-layer prologue (norms / top-NU / quantisation) and the
+ * last weight row. Values are of the LAST layer of the most recent M=1 decode call, read from
+ * CTA 0; the call synchronises the handle's last stream. With SP_MOE_TIMING=1 the host entry
+ * sp_moe_forward also prints one `[g4-moe] TIMING` line to stderr every 300 decoded layers. */
+typedef struct {
+    float wait_us[3];      /* kernel entry -> predecessor's results visible (0: router + shared gate/up, 1: top-NU + shared down + routed gate|up, 2: routed down + combine) */
+    float prologue_us[3];  /* -> activations normalised / selected / quantised in shared memory */
+    float rows_us[3];      /* -> last weight row of the CTA's slice done */
+    float layer_us;        /* first kernel's entry -> last kernel's last row */
+    float raw_us[3][8];    /* every stamp a kernel took, microseconds since the first kernel's entry (0 = not taken) */
+} sp_moe_timing;
+int sp_moe_decode_timing(sp_moe *h, sp_moe_timing *out);
+
+/* Failure-path probe: runs one CTA that waits on a copy that is never started, with a limit of
+ * `polls` polls (1..1048576). The wait gives up, the kernel returns normally and records the same
+ * error word a real timed-out wait in the decode kernels records, so the next sp_moe_status call
+ * returns SP_MOE_ECUDA with the timeout text, and the handle stays usable. Nothing traps or hangs.
+ * (The reference's model for this is the bounded handshake of tools/moe_cpu_bench/handshake_test.cu:14-41.) */
+int sp_moe_debug_wait_timeout(sp_moe *h, int polls, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

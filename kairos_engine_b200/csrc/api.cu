@@ -54,13 +54,8 @@ struct sp_moe {
     SpLayerDev *layers_dev;     /* device array [n_layers] */
     std::vector<SpLayerDev> layers_host;
     std::vector<unsigned char> has_bias, uploaded;
-    /* decode scratch */
-    unsigned long long *xch;    /* exchange words: logits | hd | dn | h | acc */
-    size_t xch_words;
     int *status;
     int *status_host;           /* page-locked copy target: one synchronisation reads the error word */
-    unsigned epoch;
-    int dec_grid, dec_slots; size_t dec_smem;
     /* host-pointer entry staging */
     float *x_dev, *y_dev; int32_t *sel_dev; float *wts_dev;
     SpBatchedScratch bs;
@@ -71,7 +66,11 @@ struct sp_moe {
     struct BatchGraph { int lf, nl, M, flavour; bool routing; cudaGraphExec_t exec; int launches; };
     std::vector<BatchGraph> bgraphs;
     SpGraphScratch gs; unsigned char *gs_base; float *g_x, *g_y; int32_t *g_sel; float *g_wts;
-    int decode_impl;            /* 0 = CUDA graph of three kernels per layer, 1 = one persistent kernel */
+    int decode_impl;            /* 0 = rows staged through shared memory (decode_staged.cu), 1 = rows read directly (decode_graph.cu) */
+    unsigned staged_flags;
+    long long *stamps;          /* device time stamps of the last layer of a decode run (SP_MOE_TIMING=1), else NULL */
+    long long *stamps_host;
+    uint64_t timing_runs; double timing_us[3][4], timing_layer_us;
     int sms;
     cudaStream_t stream;        /* stream of the host-pointer entry */
     cudaStream_t last_stream;
@@ -149,9 +148,6 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
     OPEN_CK(cudaMemcpy(h->layers_dev, h->layers_host.data(), sizeof(SpLayerDev) * c.n_layers, cudaMemcpyHostToDevice), "layer table H2D");
     size_t sb = 0;
     auto dalloc = [&](void **p, size_t bytes) { sb += up256(bytes); return cudaMalloc(p, bytes); };
-    h->xch_words = (size_t)c.NE + c.FFS + c.E + (size_t)c.NU * c.FFE + c.E;
-    OPEN_CK(dalloc((void **)&h->xch, 8 * h->xch_words), "scratch");
-    OPEN_CK(cudaMemset(h->xch, 0, 8 * h->xch_words), "memset");
     OPEN_CK(dalloc((void **)&h->status, 256), "scratch");
     OPEN_CK(cudaMemset(h->status, 0, 256), "memset");
     OPEN_CK(cudaMallocHost((void **)&h->status_host, 64), "status word (host)");
@@ -173,26 +169,29 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         h->gs.xbuf[0] = (float *)(b + o_x0); h->gs.xbuf[1] = (float *)(b + o_x1);
         h->gs.prev_post_ffw1 = h->gs.prev_post_ffw2 = h->gs.prev_post_ffw = nullptr;
         h->g_x = (float *)(b + o_gx); h->g_y = (float *)(b + o_gy); h->g_sel = (int32_t *)(b + o_gsel); h->g_wts = (float *)(b + o_gw);
-        const char *ev = getenv("SP_MOE_DECODE_IMPL");          /* house convention: behaviour switches are SP_* variables read once */
-        h->decode_impl = (ev && ev[0] == 'p') ? 1 : 0;
         cudaDeviceGetAttribute(&h->sms, cudaDevAttrMultiProcessorCount, c.device);
+        int optin = 0;
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
+        /* house convention: behaviour switches are SP_* variables read once. SP_MOE_DECODE_IMPL=direct keeps the
+         * weight rows out of shared memory (the path every geometry can take); the default stages them when they fit. */
+        const char *ev = getenv("SP_MOE_DECODE_IMPL");
+        h->decode_impl = ((ev && ev[0] == 'd') || !sp_staged_fits(h->d, h->sms, (size_t)optin)) ? 1 : 0;
+        const char *fv = getenv("SP_MOE_STAGED_FLAGS");
+        h->staged_flags = fv ? (unsigned)strtoul(fv, nullptr, 0) : (unsigned)SP_STAGED_DEFAULT;
+        /* the kernels' shared-memory limits are a per-device setting: set them for this handle's device */
+        OPEN_CK(sp_graph_prepare(), "decode kernel attributes");
+        if (h->decode_impl == 0) OPEN_CK(sp_staged_prepare(h->d, h->sms), "decode kernel attributes");
+        const char *tv = getenv("SP_MOE_TIMING");                 /* the reference's switch for its [g4-moe] TIMING line (CF:7186-7201) */
+        if (tv && tv[0] == '1') {
+            OPEN_CK(dalloc((void **)&h->stamps, 24 * sizeof(long long)), "timing stamps");
+            OPEN_CK(cudaMemset(h->stamps, 0, 24 * sizeof(long long)), "memset");
+            OPEN_CK(cudaMallocHost((void **)&h->stamps_host, 24 * sizeof(long long)), "timing stamps (host)");
+        }
     }
     { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, c.max_expert_rows, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
     OPEN_CK(cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     h->last_stream = h->stream;
     h->scratch_bytes = sb;
-    /* persistent decode kernel: one CTA per SM, co-resident */
-    {
-        int sms = 0, optin = 0;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device);
-        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, c.device);
-        h->dec_slots = sp_decode_slots(h->d, sms, (size_t)optin, &h->dec_smem);
-        if (h->dec_slots < 2) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM's shared memory (%d B)", optin); }
-        int grid = 0;
-        OPEN_CK(sp_decode_prepare(h->d, h->dec_smem, &grid), "decode kernel attributes");
-        if (grid <= 0) { sp_moe_close(h); return fail(SP_MOE_EUNSUPPORTED, "sp_moe_open: decode kernel does not fit an SM (%zu B shared memory)", h->dec_smem); }
-        h->dec_grid = grid;
-    }
 #undef OPEN_CK
     *out = h;
     return SP_MOE_OK;
@@ -205,9 +204,10 @@ extern "C" int sp_moe_close(sp_moe *h) {
     sp_batched_free(&h->bs);
     for (auto &g : h->graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
     for (auto &g : h->bgraphs) if (g.exec) cudaGraphExecDestroy(g.exec);
-    void *ps[] = {h->gs_base, h->arena, h->layers_dev, h->xch, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev};
+    void *ps[] = {h->gs_base, h->arena, h->layers_dev, h->status, h->x_dev, h->y_dev, h->sel_dev, h->wts_dev, h->stamps};
     for (void *p : ps) if (p) cudaFree(p);
     if (h->status_host) cudaFreeHost(h->status_host);
+    if (h->stamps_host) cudaFreeHost(h->stamps_host);
     cudaGetLastError();
     delete h;
     return SP_MOE_OK;
@@ -239,6 +239,11 @@ static int upload(sp_moe *h, int L, const sp_moe_layer_weights *w, cudaMemcpyKin
 #undef UP
     h->has_bias[L] = w->router_bias != nullptr;
     h->layers_host[L] = layer_view(h, L, h->has_bias[L]);
+    /* captured graphs hold this layer's view by value (the bias pointer may just have appeared or gone) */
+    for (size_t i = h->graphs.size(); i-- > 0;)
+        if (L >= h->graphs[i].lf && L < h->graphs[i].lf + h->graphs[i].nl) { cudaGraphExecDestroy(h->graphs[i].exec); h->graphs.erase(h->graphs.begin() + (long)i); }
+    for (size_t i = h->bgraphs.size(); i-- > 0;)
+        if (L >= h->bgraphs[i].lf && L < h->bgraphs[i].lf + h->bgraphs[i].nl) { cudaGraphExecDestroy(h->bgraphs[i].exec); h->bgraphs.erase(h->bgraphs.begin() + (long)i); }
     CK(cudaMemcpy(h->layers_dev + L, &h->layers_host[L], sizeof(SpLayerDev), cudaMemcpyHostToDevice), who);
     h->uploaded[L] = 1;
     return SP_MOE_OK;
@@ -263,7 +268,7 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream;
     h->last_stream = st;
-    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE && h->decode_impl == 0) {
+    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
         const bool routing = sel_dev || wts_dev;
         sp_moe::DecodeGraph *dg = nullptr;
         for (auto &g : h->graphs) if (g.lf == lf && g.nl == nl && g.routing == routing) dg = &g;
@@ -272,8 +277,11 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
             cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr; int nlaunch = 0;
             CK(cudaStreamSynchronize(cs), "stream synchronize");
             CK(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal), "begin capture");
-            cudaError_t e = sp_graph_decode_enqueue(h->d, h->layers_host.data(), lf, nl, h->g_x, h->g_y, routing ? h->g_sel : nullptr,
-                                                    routing ? h->g_wts : nullptr, h->gs, h->sms, cs, true, &nlaunch);
+            cudaError_t e = h->decode_impl == 0
+                ? sp_staged_decode_enqueue(h->d, h->layers_host.data(), lf, nl, h->g_x, h->g_y, routing ? h->g_sel : nullptr,
+                                           routing ? h->g_wts : nullptr, h->gs, h->sms, h->staged_flags, h->stamps, cs, true, &nlaunch)
+                : sp_graph_decode_enqueue(h->d, h->layers_host.data(), lf, nl, h->g_x, h->g_y, routing ? h->g_sel : nullptr,
+                                          routing ? h->g_wts : nullptr, h->gs, h->sms, cs, true, &nlaunch);
             cudaError_t e2 = cudaStreamEndCapture(cs, &graph);
             if (e != cudaSuccess || e2 != cudaSuccess) { if (graph) cudaGraphDestroy(graph); cudaGetLastError(); return fail_cuda(e != cudaSuccess ? e : e2, "decode graph capture"); }
             e = cudaGraphInstantiate(&exec, graph, 0);
@@ -289,34 +297,6 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
         if (sel_dev) CK(cudaMemcpyAsync(sel_dev, h->g_sel, ns, cudaMemcpyDeviceToDevice, st), "sel staging");
         if (wts_dev) CK(cudaMemcpyAsync(wts_dev, h->g_wts, ns, cudaMemcpyDeviceToDevice, st), "wts staging");
         h->launches += (uint64_t)dg->launches;
-        return SP_MOE_OK;
-    }
-    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
-        /* at most 64 layers per launch (the bias mask is one word): longer runs chain launches */
-        const float *xin = x_dev;
-        for (int l0 = lf; l0 < lf + nl; l0 += 64) {
-        const int cnt = (lf + nl - l0) < 64 ? (lf + nl - l0) : 64;
-        SpDecodeArgs a;
-        a.layer0 = layer_view(h, 0, true); a.layer_stride = h->layer_bytes; a.bias_mask = 0;
-        for (int i = 0; i < cnt; i++) if (h->has_bias[l0 + i]) a.bias_mask |= 1ull << i;
-        a.layer_first = l0; a.n_layers = cnt; a.d = h->d;
-        a.x_in = xin; a.y_out = y_dev;
-        a.sel_out = sel_dev ? sel_dev + (size_t)(l0 - lf) * h->cfg.NU : nullptr;
-        a.wts_out = wts_dev ? wts_dev + (size_t)(l0 - lf) * h->cfg.NU : nullptr;
-        const int nl_launch = cnt;
-        if (h->epoch > 0xFFFFFFFFu - (unsigned)nl_launch - 2u) {      /* epoch wrap: start over on clean words */
-            CK(cudaMemsetAsync(h->xch, 0, 8 * h->xch_words, st), "memset");
-            h->epoch = 0;
-        }
-        unsigned long long *x = h->xch;
-        a.x_logits = x; x += h->cfg.NE; a.x_hd = x; x += h->cfg.FFS; a.x_dn = x; x += h->cfg.E;
-        a.x_h = x; x += (size_t)h->cfg.NU * h->cfg.FFE; a.x_acc = x;
-        a.status = h->status; a.epoch_base = h->epoch; a.n_slots = h->dec_slots;
-        h->epoch += (unsigned)nl_launch;
-        CK(sp_decode_launch(a, h->dec_grid, h->dec_smem, st), "decode kernel launch");
-        h->launches += 1;
-        xin = y_dev;
-        }
         return SP_MOE_OK;
     }
     if (M <= 64) {
@@ -452,6 +432,71 @@ extern "C" int sp_moe_status(sp_moe *h) {
     return fail(SP_MOE_ECUDA, "gemma4-MoE: kernel error word %d", st);
 }
 
+/* ---------------------------------------------------------------- phase timing (SP_MOE_TIMING=1) */
+static int read_timing(sp_moe *h, sp_moe_timing *t) {
+    CK(cudaMemcpyAsync(h->stamps_host, h->stamps, 24 * sizeof(long long), cudaMemcpyDeviceToHost, h->last_stream), "timing D2H");
+    CK(cudaStreamSynchronize(h->last_stream), "stream synchronize");
+    const long long *s = h->stamps_host;
+    for (int k = 0; k < 3; k++) {
+        t->wait_us[k] = (float)((s[k * 8 + 1] - s[k * 8 + 0]) * 1e-3);
+        t->prologue_us[k] = (float)((s[k * 8 + 3] - s[k * 8 + 1]) * 1e-3);
+        t->rows_us[k] = (float)((s[k * 8 + 4] - s[k * 8 + 3]) * 1e-3);
+    }
+    t->layer_us = (float)((s[2 * 8 + 4] - s[0]) * 1e-3);
+    for (int k = 0; k < 3; k++) for (int i = 0; i < 8; i++) t->raw_us[k][i] = s[k * 8 + i] ? (float)((s[k * 8 + i] - s[0]) * 1e-3) : 0.0f;
+    return SP_MOE_OK;
+}
+extern "C" int sp_moe_decode_timing(sp_moe *h, sp_moe_timing *out) {
+    if (!h || !out) return fail(SP_MOE_EBADARG, "sp_moe_decode_timing: NULL argument");
+    if (!h->stamps) return fail(SP_MOE_EBADSTATE, "sp_moe_decode_timing: open the handle with SP_MOE_TIMING=1 in the environment");
+    if (h->decode_impl != 0) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_decode_timing: only the shared-memory-staged decode path records phases");
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    return read_timing(h, out);
+}
+/* the reference prints its line every 300 router syncs = 10 tokens x 30 layers (CF:9022); same cadence in decoded layers */
+static void timing_accumulate(sp_moe *h, int nl) {
+    sp_moe_timing t;
+    if (!h->stamps || h->decode_impl != 0 || read_timing(h, &t) != SP_MOE_OK) return;
+    for (int k = 0; k < 3; k++) { h->timing_us[k][0] += t.wait_us[k]; h->timing_us[k][1] += t.prologue_us[k]; h->timing_us[k][2] += t.rows_us[k]; h->timing_us[k][3] += 1.0; }
+    h->timing_layer_us += t.layer_us;
+    const uint64_t before = h->timing_runs; h->timing_runs += (uint64_t)nl;
+    if (before / 300 != h->timing_runs / 300) {
+        const double n = h->timing_us[0][3] > 0 ? h->timing_us[0][3] : 1.0;
+        std::fprintf(stderr, "    [g4-moe] TIMING after %llu decoded layers (last layer of each call sampled, device clock): layer %.1f us | "
+                             "router+shared: wait %.1f prologue %.1f rows %.1f | top-k+gate|up: wait %.1f prologue %.1f rows %.1f | "
+                             "down+combine: wait %.1f prologue %.1f rows %.1f\n",
+                     (unsigned long long)h->timing_runs, h->timing_layer_us / n,
+                     h->timing_us[0][0] / n, h->timing_us[0][1] / n, h->timing_us[0][2] / n,
+                     h->timing_us[1][0] / n, h->timing_us[1][1] / n, h->timing_us[1][2] / n,
+                     h->timing_us[2][0] / n, h->timing_us[2][1] / n, h->timing_us[2][2] / n);
+        std::fflush(stderr);
+    }
+}
+
+/* ---------------------------------------------------------------- failure-path probe */
+__global__ void k_wait_timeout_probe(int polls, int *status) {
+    __shared__ unsigned long long bar;
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr) : "memory");
+    /* nothing ever arrives on this barrier: the wait below can only run out */
+    for (int i = 0; i < polls; i++) {
+        unsigned ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(addr) : "memory");
+        if (ok) return;
+    }
+    atomicExch(status, SP_KERR_BARRIER_TIMEOUT);
+}
+extern "C" int sp_moe_debug_wait_timeout(sp_moe *h, int polls, void *stream) {
+    if (!h) return fail(SP_MOE_EBADARG, "sp_moe_debug_wait_timeout: NULL handle");
+    if (polls < 1 || polls > (1 << 20)) return fail(SP_MOE_EBADARG, "sp_moe_debug_wait_timeout: polls=%d outside [1, 1048576]", polls);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    cudaStream_t st = (cudaStream_t)stream; h->last_stream = st;
+    k_wait_timeout_probe<<<1, 1, 0, st>>>(polls, h->status);
+    h->launches += 1;
+    CK(cudaGetLastError(), "wait-timeout probe launch");
+    return SP_MOE_OK;
+}
+
 extern "C" int sp_moe_forward(sp_moe *h, int lf, int nl, int flavour, int M,
                               const float *x, float *y, int32_t *sel, float *wts) {
     int rc = check_forward(h, lf, nl, flavour, M, x, y, "sp_moe_forward");
@@ -464,5 +509,7 @@ extern "C" int sp_moe_forward(sp_moe *h, int lf, int nl, int flavour, int M,
     CK(cudaMemcpyAsync(y, h->y_dev, nx, cudaMemcpyDeviceToHost, h->stream), "y D2H");
     if (sel) CK(cudaMemcpyAsync(sel, h->sel_dev, ns, cudaMemcpyDeviceToHost, h->stream), "sel D2H");
     if (wts) CK(cudaMemcpyAsync(wts, h->wts_dev, ns, cudaMemcpyDeviceToHost, h->stream), "wts D2H");
-    return sp_moe_status(h);
+    rc = sp_moe_status(h);
+    if (rc == SP_MOE_OK && M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) timing_accumulate(h, nl);
+    return rc;
 }

@@ -333,8 +333,14 @@ template <bool FA, bool PAIR, int NIT>
 __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
-    const int first = g.offset ? g.offset[grp] : 0;
-    const int cnt = g.offset ? g.offset[grp + 1] - first : (g.count ? g.count[grp] : g.M);
+    int first = 0, cnt;
+    if (g.offset) {                      /* caller-supplied ranges: keep them inside the g.M rows that exist */
+        int last = g.offset[grp + 1];
+        first = g.offset[grp];
+        first = first < 0 ? 0 : (first > g.M ? g.M : first);
+        last = last > g.M ? g.M : last;
+        cnt = last - first;
+    } else cnt = g.count ? g.count[grp] : g.M;
     if (cnt <= 0) return;
     const int r = blockIdx.x * 8 + warp;
     if (r >= g.rows) return;
@@ -500,15 +506,25 @@ __global__ void __launch_bounds__(256) k_b_recv_layout(const int *counts_all, in
     int *cnt = lsm, *sorted_start = lsm + nb, *arrival_start = lsm + 2 * nb + 1;
     for (int b = threadIdx.x; b < nb; b += 256) cnt[b] = counts_all[(b % n_ranks) * NE + e0 + b / n_ranks];
     __syncthreads();
+    /* A source whose block for this rank overflowed kept only its first `capacity` rows, in expert order
+     * (k_b_dispatch_rows drops the rest and sets the error word) but still reports its full counts: clamp
+     * each source's running total to the capacity, so every index below stays inside the receive buffer. */
+    for (int s_ = threadIdx.x; s_ < n_ranks; s_ += 256) {
+        int a = 0;
+        for (int e = 0; e < epr; e++) {
+            int c = cnt[e * n_ranks + s_];
+            c = c < 0 ? 0 : c;
+            if (c > capacity - a) c = capacity - a;
+            cnt[e * n_ranks + s_] = c;
+            arrival_start[e * n_ranks + s_] = s_ * capacity + a;
+            a += c;
+        }
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;
         for (int b = 0; b < nb; b++) { sorted_start[b] = acc; acc += cnt[b]; }
         sorted_start[nb] = acc;
-    }
-    if (threadIdx.x >= 32 && threadIdx.x < 32 + n_ranks) {
-        const int s_ = threadIdx.x - 32;
-        int a = s_ * capacity;
-        for (int e = 0; e < epr; e++) { arrival_start[e * n_ranks + s_] = a; a += cnt[e * n_ranks + s_]; }
     }
     __syncthreads();
     const int total = sorted_start[nb];

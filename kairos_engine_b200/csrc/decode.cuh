@@ -1,36 +1,9 @@
-/* decode.cuh — launch interface of the persistent M=1 decode kernel (decode.cu). */
+/* decode.cuh — launch interfaces of the M=1 decode paths: three kernels per layer replayed from a
+ * CUDA graph, with the weight rows staged through shared memory by the copy engine
+ * (decode_staged.cu, the default) or read by the warps directly (decode_graph.cu, any geometry). */
 #pragma once
 #include "common.cuh"
 
-struct SpDecodeArgs {
-    SpLayerDev layer0;             /* device pointers of layer 0 (router_bias always set: see bias_mask) */
-    size_t layer_stride;           /* bytes between consecutive layers' slabs */
-    unsigned long long bias_mask;  /* bit li: layer layer_first + li has a router bias (n_layers <= 64 per launch) */
-    int layer_first, n_layers;
-    SpDims d;
-    const float *x_in;             /* [E] */
-    float *y_out;                  /* [E] */
-    int32_t *sel_out;              /* [n_layers][NU] descending-p ids, or NULL */
-    float *wts_out;                /* [n_layers][NU], or NULL */
-    /* exchange buffers in device memory: 8-byte {f32 value, u32 epoch} words, written by the
-     * CTA that owns the element and polled by every CTA; zero-initialised, epochs start at 1 */
-    unsigned long long *x_logits;  /* [NE] */
-    unsigned long long *x_hd;      /* [FFS]      shared-expert GeGLU output */
-    unsigned long long *x_dn;      /* [E]        shared-expert down output */
-    unsigned long long *x_h;       /* [NU][FFE]  routed GeGLU outputs, ascending-id slots */
-    unsigned long long *x_acc;     /* [E]        combined routed output */
-    int *status;                   /* SP_KERR_* */
-    unsigned epoch_base;           /* layer li of this launch publishes epoch_base + li + 1 */
-    int n_slots;                   /* ring slots that fit the dynamic shared memory */
-};
-
-/* ring slots and total dynamic shared memory for these dims under `smem_limit`; 0 if it cannot fit */
-int sp_decode_slots(const SpDims &d, int grid, size_t smem_limit, size_t *smem_bytes);
-int sp_decode_threads();
-cudaError_t sp_decode_prepare(const SpDims &d, size_t smem, int *max_grid);
-cudaError_t sp_decode_launch(const SpDecodeArgs &args, int grid, size_t smem, cudaStream_t st);
-
-/* ---- the three-kernels-per-layer decode path (decode_graph.cu) ---- */
 struct SpGraphScratch {
     float *logits, *hd, *dn, *h, *acc;          /* [NE] [FFS] [E] [NU*FFE] [E] */
     signed char *in_q; float *in_s; int *in_c;  /* the routed experts' quantised input, [E] / [E/16] */
@@ -39,6 +12,28 @@ struct SpGraphScratch {
     float *xbuf[2];                             /* residual between layers, ping-pong */
     const float *prev_post_ffw1, *prev_post_ffw2, *prev_post_ffw;   /* set per launch */
 };
-size_t sp_graph_scratch_bytes(const SpDims &d);
+
+/* ---- decode_graph.cu ---- */
+/* per device, before the first enqueue: the kernels' dynamic shared-memory limits */
+cudaError_t sp_graph_prepare();
 cudaError_t sp_graph_decode_enqueue(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl, const float *x_in, float *y_out,
                                     int32_t *sel, float *wts, const SpGraphScratch &sc, int sms, cudaStream_t st, bool pdl, int *nlaunch);
+/* recombine of the last layer of a run (one CTA): y = x_prev + post_ffw-normed branch sum */
+cudaError_t sp_graph_launch_finish(const SpDims &d, const SpLayerDev &last, const SpGraphScratch &sc, const float *x_prev, float *y_out,
+                                   cudaStream_t st, bool pdl);
+
+/* ---- decode_staged.cu ---- */
+enum {
+    SP_STAGED_PREFETCH_SD = 1,      /* K1 asks L2 for the shared-expert down rows K2 will stage */
+    SP_STAGED_PREFETCH_DN = 2,      /* K2 asks L2 for the routed down rows K3 will stage */
+    SP_STAGED_PREFETCH_NEXT = 4,    /* K3 asks L2 for the next layer's router rows and shared gate/up rows */
+    SP_STAGED_DEFAULT = 7
+};
+/* true when one CTA's slice of every phase fits `smem_optin` bytes of shared memory on a grid of `sms` CTAs */
+bool sp_staged_fits(const SpDims &d, int sms, size_t smem_optin);
+cudaError_t sp_staged_prepare(const SpDims &d, int sms);
+/* stamps: NULL, or 24 device words that receive CTA 0's globaltimer readings in the last layer of the run:
+ * [kernel 0..2][0 entry, 1 predecessor done, 2 mid-prologue, 3 prologue done, 4 rows done] */
+cudaError_t sp_staged_decode_enqueue(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl, const float *x_in, float *y_out,
+                                     int32_t *sel, float *wts, const SpGraphScratch &sc, int sms, unsigned flags, long long *stamps,
+                                     cudaStream_t st, bool pdl, int *nlaunch);

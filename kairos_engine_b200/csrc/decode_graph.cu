@@ -1,9 +1,14 @@
-/* decode_graph.cu — the M=1 decode path as three kernels per layer, replayed from a CUDA graph.
+/* decode_graph.cu — the M=1 decode path as three kernels per layer, replayed from a CUDA graph,
+ * weight rows read by the warps straight from global memory. Works for every geometry the handle
+ * accepts; decode_staged.cu is the faster form for geometries whose per-CTA slices fit shared
+ * memory.
  *
- * Same work and the same arithmetic as the persistent kernel in decode.cu (which see for the
- * reference lines each step follows; CF = src/backends/cuda/cuda_forward.cu), cut at the three
- * points where every CTA needs every other CTA's results, so the kernel boundary is the grid-wide
- * exchange and each kernel runs at full occupancy with plain streaming loads:
+ * Replaces, for n_tok == 1, the ~20 launches + one host round trip per layer of g4_ffn_apply
+ * (CF:8314-9050 of src/backends/cuda/cuda_forward.cu): k_rmsnorm, gemv_w_packed x3 (shared
+ * expert), k_gelu_mul, k_moe_router_prep, router SGEMM, D2H + moe_topk_host, k_quant_act_int8,
+ * k_gemv_q4b_dp4a_grp x2, k_moe_gelu_split_batch, k_moe_combine_ord and the recombine norms.
+ * The layer is cut at the three points where every CTA needs every other CTA's results, so the
+ * kernel boundary is the grid-wide exchange:
  *
  *   K1  [recombine of the previous layer] -> norms of x, int8 quantisation, router input
  *       router rows (fp32) + shared-expert gate/up row pairs            -> logits, hd
@@ -21,13 +26,6 @@
 #include "common.cuh"
 #include "decode.cuh"
 
-#ifdef SP_DECODE_STAMPS
-__device__ long long g_dg_stamps[4 * 16];
-#define GSTAMP(k, i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_dg_stamps[(k) * 16 + (i)] = t_; } } while (0)
-extern "C" int sp_debug_read_dg_stamps(long long *out) { return (int)cudaMemcpyFromSymbol(out, g_dg_stamps, sizeof(long long) * 64); }
-#else
-#define GSTAMP(k, i) do { } while (0)
-#endif
 
 namespace {
 
@@ -49,7 +47,7 @@ struct GArgs {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-/* sum over the CTA in double: shuffle tree per warp, warp totals in order (see decode.cu block_sum) */
+/* sum over the CTA in double: shuffle tree per warp, warp totals in order */
 __device__ __forceinline__ double cta_sum(double v, double *sh) {
     v = warp_sum_f64(v);
     if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
@@ -174,9 +172,7 @@ __global__ void __launch_bounds__(kT, 1) k_dg_router_shared(GArgs a) {
                 l2_prefetch(L.sg_bs + c * (E / 32), E / 16, lane); l2_prefetch(L.su_bs + c * (E / 32), E / 16, lane); }
         }
     }
-    GSTAMP(0, 0);
     pdl_wait();
-    GSTAMP(0, 1);
     float x[KE];
     if (a.first) {
 #pragma unroll
@@ -212,7 +208,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_router_shared(GArgs a) {
 #pragma unroll
         for (int k = 0; k < KE; k++) { const int i = t + kT * k; if (i < E) a.x_cur[i] = x[k]; }
     }
-    GSTAMP(0, 2);
     /* A: norms of x (CF:8347, 8402-8404, 8425) */
     double part = 0.0;
 #pragma unroll
@@ -238,7 +233,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_router_shared(GArgs a) {
     }
     __syncthreads();
     pdl_launch();
-    GSTAMP(0, 3);
     {   /* the next kernel's routing-independent rows (shared-expert down): ask L2 for them now */
         const int j0 = (int)((long long)b * E / G), nj = (int)((long long)(b + 1) * E / G) - j0;
         if (warp == kW - 1) { l2_prefetch(L.sd_codes + (size_t)j0 * (d.FFS / 2), nj * (d.FFS / 2), lane); l2_prefetch(L.sd_bs + (size_t)j0 * (d.FFS / 32), nj * (d.FFS / 16), lane); }
@@ -277,7 +271,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_router_shared(GArgs a) {
         }
     }
     __syncthreads();
-    GSTAMP(0, 4);
 }
 
 /* moe_topk_host (CF:6220-6240), whole CTA */
@@ -341,9 +334,7 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_up(GArgs a) {
     const SpLayerDev &L = a.L;
     float *dsc = p + NE;                                  /* [NE] per-expert down scales */
     for (int i = t; i < NE; i += kT) dsc[i] = __ldg(L.dexps_scale + i);      /* weights: before the wait */
-    GSTAMP(1, 0);
     pdl_wait();
-    GSTAMP(1, 1);
     /* the activations this CTA needs, requested in one batch before the top-k chain */
     for (int i = t; i < E / 16; i += kT) { reinterpret_cast<int4 *>(q_in)[i] = __ldcg(reinterpret_cast<const int4 *>(a.s.in_q) + i); s_in[i] = __ldcg(a.s.in_s + i); c_in[i] = __ldcg(a.s.in_c + i); }
     {
@@ -355,7 +346,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_up(GArgs a) {
             for (int i = 0; i < 16; i++) hv[i] = __ldcg(a.s.hd + 16 * bq0 + i);
         }
         topk_cta(a.s.logits, d, dsc, lg, ex, p, red, sel_desc, p_desc, sel_asc, cw, a.s.status);
-        GSTAMP(1, 2);
         if (mine) quant_block16_store(hv, reinterpret_cast<int4 *>(q_hd) + bq0, s_hd + bq0, c_hd + bq0);
         for (int bq = bq0 + kT; bq < nbh; bq += kT) {      /* only when FFS/16 exceeds the CTA */
             float v[16];
@@ -371,7 +361,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_up(GArgs a) {
     }
     __syncthreads();
     pdl_launch();
-    GSTAMP(1, 3);
     {   /* the routed down rows the next kernel will read in this CTA's slice: known now, ask L2 for them */
         const int j0p = (int)((long long)b * E / G), njp = (int)((long long)(b + 1) * E / G) - j0p;
         for (int sl = warp; sl < NU; sl += kW) {
@@ -426,7 +415,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_up(GArgs a) {
             }
         } });
     __syncthreads();
-    GSTAMP(1, 4);
 }
 
 /* ---------------------------------------------------------------- K3 */
@@ -441,14 +429,11 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_down(GArgs a) {
     float *out = reinterpret_cast<float *>(c_h + nblk);                   /* [NU][rows_max] */
     int *sel_asc = reinterpret_cast<int *>(out + (size_t)NU * rows_max); float *cw = reinterpret_cast<float *>(sel_asc + SP_MAX_NU);
     const SpLayerDev &L = a.L;
-    GSTAMP(2, 0);
     pdl_wait();
-    GSTAMP(2, 1);
     quant_blocks(NU * FFE, q_h, s_h, c_h, [&](int i) { return __ldcg(a.s.h + i); });
     if (t < NU) { sel_asc[t] = __ldcg(a.s.sel_asc + t); cw[t] = __ldcg(a.s.cw + t); }
     __syncthreads();
     pdl_launch();
-    GSTAMP(2, 3);
     if (a.has_next) {   /* the next layer's router rows and shared gate/up pairs of this CTA's slice */
         const SpLayerDev &N = a.Ln;
         const int r0 = (int)((long long)b * d.NE / G), nr = (int)((long long)(b + 1) * d.NE / G) - r0;
@@ -510,7 +495,6 @@ __global__ void __launch_bounds__(kT, 1) k_dg_experts_down(GArgs a) {
         for (int k = 0; k < NU; k++) acc = __fadd_rn(acc, __fmul_rn(cw[k], out[k * rows_max + jj]));
         a.s.acc[j0 + jj] = acc;
     }
-    GSTAMP(2, 4);
 }
 
 /* ---------------------------------------------------------------- KF: recombine of the last layer (CF:9014-9019) */
@@ -562,8 +546,20 @@ cudaError_t launch_pdl(K kernel, int grid, size_t smem, cudaStream_t st, bool pd
 
 }  // namespace
 
-size_t sp_graph_scratch_bytes(const SpDims &d) {
-    return 256 * 16 + 4 * ((size_t)d.NE + d.FFS + 3 * (size_t)d.E + (size_t)d.NU * d.FFE + 2 * (size_t)(d.E / 16) + 4 * SP_MAX_NU) + d.E + 4096;
+cudaError_t sp_graph_prepare() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(k_dg_router_shared<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_dg_router_shared<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_dg_experts_up, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_dg_experts_down, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+}
+
+cudaError_t sp_graph_launch_finish(const SpDims &d, const SpLayerDev &last, const SpGraphScratch &sc, const float *x_prev, float *y_out,
+                                   cudaStream_t st, bool pdl) {
+    GArgs a{};
+    a.d = d; a.s = sc; a.x_prev = x_prev;
+    a.s.prev_post_ffw1 = last.post_ffw1; a.s.prev_post_ffw2 = last.post_ffw2; a.s.prev_post_ffw = last.post_ffw;
+    return launch_pdl(k_dg_finish, 1, 32 * 8 + 64, st, pdl, a, y_out);
 }
 
 /* Enqueues layers [lf, lf+nl) for one token on `st` (capturable into a CUDA graph). */
@@ -575,16 +571,6 @@ cudaError_t sp_graph_decode_enqueue(const SpDims &d, const SpLayerDev *layers_ho
     const size_t sm2 = (size_t)E + FFS + 2 * ((size_t)(E / 16) + FFS / 16) * 4 + 8 + 48 * 8 + (size_t)NE * 8 + 3 * (size_t)NE * 4 + 4 * SP_MAX_NU * 4 + 64;
     const int rows_max = (E + grid - 1) / grid + 1;
     const size_t sm3 = (size_t)NU * FFE + 2 * (size_t)((NU * FFE) >> 4) * 4 + (size_t)NU * rows_max * 4 + 2 * SP_MAX_NU * 4 + 64;
-    const size_t smf = 32 * 8 + 64;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(k_dg_router_shared<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        cudaFuncSetAttribute(k_dg_router_shared<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        cudaFuncSetAttribute(k_dg_experts_up, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        cudaFuncSetAttribute(k_dg_experts_down, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        cudaFuncSetAttribute(k_dg_finish, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        attr_done = true;
-    }
     if (sm1 > 100 * 1024 || sm2 > 100 * 1024 || sm3 > 100 * 1024) return cudaErrorInvalidValue;
     cudaError_t e = cudaSuccess;
     for (int li = 0; li < nl && e == cudaSuccess; li++) {
@@ -599,11 +585,6 @@ cudaError_t sp_graph_decode_enqueue(const SpDims &d, const SpLayerDev *layers_ho
         if (e == cudaSuccess) { e = launch_pdl(k_dg_experts_up, grid, sm2, st, pdl, a); (*nlaunch)++; }
         if (e == cudaSuccess) { e = launch_pdl(k_dg_experts_down, grid, sm3, st, pdl, a); (*nlaunch)++; }
     }
-    if (e == cudaSuccess) {
-        GArgs a{};
-        a.d = d; a.s = sc; a.x_prev = sc.xbuf[(nl - 1) & 1];
-        a.s.prev_post_ffw1 = layers_host[lf + nl - 1].post_ffw1; a.s.prev_post_ffw2 = layers_host[lf + nl - 1].post_ffw2; a.s.prev_post_ffw = layers_host[lf + nl - 1].post_ffw;
-        e = launch_pdl(k_dg_finish, 1, smf, st, pdl, a, y_out); (*nlaunch)++;
-    }
+    if (e == cudaSuccess) { e = sp_graph_launch_finish(d, layers_host[lf + nl - 1], sc, sc.xbuf[(nl - 1) & 1], y_out, st, pdl); (*nlaunch)++; }
     return e;
 }

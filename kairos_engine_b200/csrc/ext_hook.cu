@@ -11,6 +11,7 @@
  * stream, one synchronisation, one D2H of y. Only Q4B tensors are served here.
  */
 #include "common.cuh"
+#include "gemv_common.cuh"
 #include "../../include/sp_engine/moe_backend.h"
 #include <cstdio>
 #include <cstring>
@@ -19,35 +20,6 @@
 
 namespace {
 
-__global__ void k_ext_quant(const float *x, int n, signed char *q, float *sx, int *corr) {
-    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < (n >> 4); b += gridDim.x * blockDim.x) {
-        float v[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = x[16 * b + i];
-        sx[b] = quant_block16(v, q + 16 * b, corr + b);
-    }
-}
-/* k_gemv_q4b_dp4a_v2 (CF:1688-1713): warp per row, chunk c on lane c % 32, shuffle tree */
-__global__ void k_ext_gemv(const uint8_t *codes, const uint16_t *bs, int in, int out,
-                           const signed char *q, const float *sx, const int *corr, float *y) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int j = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (j >= out) return;
-    const int n32 = in >> 5;
-    const uint8_t *row = codes + (size_t)j * (in >> 1);
-    const uint16_t *rbs = bs + (size_t)j * n32;
-    const int4 *q4 = reinterpret_cast<const int4 *>(q);
-    float facc = 0.0f;
-    for (int c = lane; c < n32; c += 32) {
-        const int4 w = ld_stream16(row + 16 * (size_t)c);
-        int a0, a1;
-        q4b_chunk_dot(w, q4[2 * c], q4[2 * c + 1], corr[2 * c], corr[2 * c + 1], a0, a1);
-        const float t = __fmaf_rn((float)a0, sx[2 * c], __fmul_rn((float)a1, sx[2 * c + 1]));
-        facc = __fmaf_rn(h2f(rbs[c]), t, facc);
-    }
-    for (int o = 16; o > 0; o >>= 1) facc += __shfl_down_sync(0xffffffffu, facc, o);
-    if (lane == 0) y[j] = facc;
-}
 /* k_silu_mul (CF:1377-1383): g = (g / (1 + exp(-g))) * up */
 __global__ void k_ext_silu_mul(float *g, const float *up, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -67,14 +39,36 @@ int ext_fail(const char *msg) { sp_set_error(msg); return 1; }
 
 }  // namespace
 
+struct ExtScratch {
+    float *dX, *dG, *dU, *dDe, *dYo;                       /* x[E], gate[FF], up[FF], down[E], accumulator[E] */
+    signed char *qx, *qh; float *sx, *sh; int *cx, *ch;    /* int8 activations of x and of silu(g)*u */
+};
 struct sp_moe_ext {
     int device;
     cudaStream_t st;
     std::vector<ExtLayer> layers;
-    float *dX, *dG, *dU, *dDe, *dYo;                       /* x[E], gate[FF], up[FF], down[E], accumulator[E] */
-    signed char *qx, *qh; float *sx, *sh; int *cx, *ch;    /* int8 activations of x and of silu(g)*u */
+    ExtScratch s;
     int cap_e, cap_ff;
 };
+
+static void ext_free_scratch(ExtScratch &s) {
+    void *ps[] = {s.dX, s.dG, s.dU, s.dDe, s.dYo, s.qx, s.qh, s.sx, s.sh, s.cx, s.ch};
+    for (void *p : ps) if (p) cudaFree(p);
+    s = ExtScratch{};
+}
+/* all-or-nothing: on failure whatever was allocated is freed and `s` is left empty */
+static bool ext_alloc_scratch(ExtScratch &s, int ce, int cf) {
+    s = ExtScratch{};
+    const bool ok =
+        cudaMalloc((void **)&s.dX, 4 * (size_t)ce) == cudaSuccess && cudaMalloc((void **)&s.dG, 4 * (size_t)cf) == cudaSuccess &&
+        cudaMalloc((void **)&s.dU, 4 * (size_t)cf) == cudaSuccess && cudaMalloc((void **)&s.dDe, 4 * (size_t)ce) == cudaSuccess &&
+        cudaMalloc((void **)&s.dYo, 4 * (size_t)ce) == cudaSuccess &&
+        cudaMalloc((void **)&s.qx, (size_t)ce) == cudaSuccess && cudaMalloc((void **)&s.qh, (size_t)cf) == cudaSuccess &&
+        cudaMalloc((void **)&s.sx, 4 * (size_t)(ce / 16)) == cudaSuccess && cudaMalloc((void **)&s.sh, 4 * (size_t)(cf / 16)) == cudaSuccess &&
+        cudaMalloc((void **)&s.cx, 4 * (size_t)(ce / 16)) == cudaSuccess && cudaMalloc((void **)&s.ch, 4 * (size_t)(cf / 16)) == cudaSuccess;
+    if (!ok) { ext_free_scratch(s); cudaGetLastError(); }
+    return ok;
+}
 
 extern "C" int sp_moe_ext_open(int device, sp_moe_ext **out) {
     if (!out) return ext_fail("sp_moe_ext_open: NULL argument");
@@ -84,16 +78,10 @@ extern "C" int sp_moe_ext_open(int device, sp_moe_ext **out) {
     if (device < 0 || device >= ndev) return ext_fail("sp_moe_ext_open: device out of range");
     if (cudaSetDevice(device) != cudaSuccess) return ext_fail("sp_moe_ext_open: cudaSetDevice failed");
     sp_moe_ext *h = new sp_moe_ext();
-    h->device = device; h->dX = nullptr; h->cap_e = h->cap_ff = 0;
+    h->device = device; h->s = ExtScratch{}; h->cap_e = h->cap_ff = 0;
     if (cudaStreamCreateWithFlags(&h->st, cudaStreamNonBlocking) != cudaSuccess) { delete h; return ext_fail("sp_moe_ext_open: stream creation failed"); }
     *out = h;
     return 0;
-}
-
-static void ext_free_scratch(sp_moe_ext *h) {
-    void *ps[] = {h->dX, h->dG, h->dU, h->dDe, h->dYo, h->qx, h->qh, h->sx, h->sh, h->cx, h->ch};
-    if (h->dX) for (void *p : ps) cudaFree(p);
-    h->dX = nullptr;
 }
 
 extern "C" int sp_moe_ext_close(sp_moe_ext *h) {
@@ -101,7 +89,7 @@ extern "C" int sp_moe_ext_close(sp_moe_ext *h) {
     cudaSetDevice(h->device);
     cudaStreamSynchronize(h->st);
     for (auto &l : h->layers) { void *ps[] = {l.g_codes, l.u_codes, l.d_codes, l.g_bs, l.u_bs, l.d_bs}; for (void *p : ps) cudaFree(p); }
-    ext_free_scratch(h);
+    ext_free_scratch(h->s);
     cudaStreamDestroy(h->st);
     delete h;
     return 0;
@@ -121,15 +109,16 @@ extern "C" int sp_moe_ext_upload_experts(sp_moe_ext *h, const char *tag,
     bool ok = true;
     for (auto &u : up) { *u.p = nullptr; if (ok && (cudaMalloc(u.p, u.n) != cudaSuccess || cudaMemcpy(*u.p, u.src, u.n, cudaMemcpyHostToDevice) != cudaSuccess)) ok = false; }
     if (ok && (E > h->cap_e || FF > h->cap_ff)) {          /* scratch for the largest shapes seen so far */
-        ext_free_scratch(h);
+        /* the larger set is allocated first and swapped in only when it is complete: on failure the old
+         * scratch, its sizes and the layers uploaded earlier all stay valid */
         const int ce = E > h->cap_e ? E : h->cap_e, cf = FF > h->cap_ff ? FF : h->cap_ff;
-        ok = cudaMalloc((void **)&h->dX, 4 * (size_t)ce) == cudaSuccess && cudaMalloc((void **)&h->dG, 4 * (size_t)cf) == cudaSuccess &&
-             cudaMalloc((void **)&h->dU, 4 * (size_t)cf) == cudaSuccess && cudaMalloc((void **)&h->dDe, 4 * (size_t)ce) == cudaSuccess &&
-             cudaMalloc((void **)&h->dYo, 4 * (size_t)ce) == cudaSuccess &&
-             cudaMalloc((void **)&h->qx, (size_t)ce) == cudaSuccess && cudaMalloc((void **)&h->qh, (size_t)cf) == cudaSuccess &&
-             cudaMalloc((void **)&h->sx, 4 * (size_t)(ce / 16)) == cudaSuccess && cudaMalloc((void **)&h->sh, 4 * (size_t)(cf / 16)) == cudaSuccess &&
-             cudaMalloc((void **)&h->cx, 4 * (size_t)(ce / 16)) == cudaSuccess && cudaMalloc((void **)&h->ch, 4 * (size_t)(cf / 16)) == cudaSuccess;
-        h->cap_e = ce; h->cap_ff = cf;
+        ExtScratch fresh;
+        ok = ext_alloc_scratch(fresh, ce, cf);
+        if (ok) {
+            cudaStreamSynchronize(h->st);
+            ext_free_scratch(h->s);
+            h->s = fresh; h->cap_e = ce; h->cap_ff = cf;
+        }
     }
     if (!ok) {
         for (auto &u : up) if (*u.p) cudaFree(*u.p);
@@ -150,19 +139,19 @@ extern "C" int sp_moe_ext_moe(void *vh, const char *tag, const int *idx, const f
     for (int k = 0; k < NU; k++) if (idx[k] < 0 || idx[k] >= M->NE) { sp_set_error("sp_moe_ext_moe: expert index out of range"); return -1; }
     if (cudaSetDevice(h->device) != cudaSuccess) return -1;
     cudaStream_t st = h->st;
-    if (cudaMemcpyAsync(h->dX, x, 4 * (size_t)E, cudaMemcpyHostToDevice, st) != cudaSuccess) return -1;
-    if (cudaMemsetAsync(h->dYo, 0, 4 * (size_t)E, st) != cudaSuccess) return -1;
+    if (cudaMemcpyAsync(h->s.dX, x, 4 * (size_t)E, cudaMemcpyHostToDevice, st) != cudaSuccess) return -1;
+    if (cudaMemsetAsync(h->s.dYo, 0, 4 * (size_t)E, st) != cudaSuccess) return -1;
     const size_t grow = (size_t)FF * (E / 2), gsrow = (size_t)FF * (E / 32), drow = (size_t)E * (FF / 2), dsrow = (size_t)E * (FF / 32);
-    k_ext_quant<<<(E / 16 + 127) / 128, 128, 0, st>>>(h->dX, E, h->qx, h->sx, h->cx);       /* the same x feeds every expert's gate and up */
+    k_quant_act<<<(E / 16 + 127) / 128, 128, 0, st>>>(h->s.dX, E, h->s.qx, h->s.sx, h->s.cx);       /* the same x feeds every expert's gate and up */
     for (int k = 0; k < NU; k++) {
         const size_t e = (size_t)idx[k];
-        k_ext_gemv<<<(FF + 7) / 8, 256, 0, st>>>(M->g_codes + e * grow, M->g_bs + e * gsrow, E, FF, h->qx, h->sx, h->cx, h->dG);
-        k_ext_gemv<<<(FF + 7) / 8, 256, 0, st>>>(M->u_codes + e * grow, M->u_bs + e * gsrow, E, FF, h->qx, h->sx, h->cx, h->dU);
-        k_ext_silu_mul<<<(FF + 255) / 256, 256, 0, st>>>(h->dG, h->dU, FF);
-        k_ext_quant<<<(FF / 16 + 127) / 128, 128, 0, st>>>(h->dG, FF, h->qh, h->sh, h->ch);
-        k_ext_gemv<<<(E + 7) / 8, 256, 0, st>>>(M->d_codes + e * drow, M->d_bs + e * dsrow, FF, E, h->qh, h->sh, h->ch, h->dDe);
-        k_ext_axpy<<<(E + 255) / 256, 256, 0, st>>>(h->dYo, h->dDe, wt[k], E);
+        k_gemv_q4b<<<(FF + 7) / 8, 256, 0, st>>>(M->g_codes + e * grow, M->g_bs + e * gsrow, E, FF, h->s.qx, h->s.sx, h->s.cx, h->s.dG);
+        k_gemv_q4b<<<(FF + 7) / 8, 256, 0, st>>>(M->u_codes + e * grow, M->u_bs + e * gsrow, E, FF, h->s.qx, h->s.sx, h->s.cx, h->s.dU);
+        k_ext_silu_mul<<<(FF + 255) / 256, 256, 0, st>>>(h->s.dG, h->s.dU, FF);
+        k_quant_act<<<(FF / 16 + 127) / 128, 128, 0, st>>>(h->s.dG, FF, h->s.qh, h->s.sh, h->s.ch);
+        k_gemv_q4b<<<(E + 7) / 8, 256, 0, st>>>(M->d_codes + e * drow, M->d_bs + e * dsrow, FF, E, h->s.qh, h->s.sh, h->s.ch, h->s.dDe);
+        k_ext_axpy<<<(E + 255) / 256, 256, 0, st>>>(h->s.dYo, h->s.dDe, wt[k], E);
     }
-    if (cudaMemcpyAsync(y, h->dYo, 4 * (size_t)E, cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+    if (cudaMemcpyAsync(y, h->s.dYo, 4 * (size_t)E, cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
     return cudaStreamSynchronize(st) == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

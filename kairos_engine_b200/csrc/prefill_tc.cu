@@ -287,29 +287,46 @@ __global__ void __launch_bounds__(256) k_tc_split(const float *src, const int *g
         *reinterpret_cast<uint4 *>(lo + r * K + 8 * c) = *reinterpret_cast<const uint4 *>(l);
     }
 }
-/* activation tiles: each group's rows in the fewest tiles of at most 128 rows, evenly sized */
-__global__ void k_tc_plan(const int *offsets, int groups, int fixed_rows, int *tiles, int *n_tiles, int cap) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int n = 0;
-    for (int g = 0; g < groups; g++) {
-        const int first = offsets ? offsets[g] : 0;
-        const int cnt = offsets ? offsets[g + 1] - first : fixed_rows;
-        if (cnt <= 0) continue;
-        const int nt = (cnt + kTileN - 1) / kTileN;
-        const int per = (((cnt + nt - 1) / nt) + 15) & ~15;
-        for (int i = 0; i < nt && n < cap; i++) {
-            const int left = cnt - i * per;
-            if (left <= 0) break;
-            tiles[3 * n] = g; tiles[3 * n + 1] = first + i * per; tiles[3 * n + 2] = left < per ? left : per; n++;
-        }
-    }
-    *n_tiles = n;
+/* block-wide inclusive scan of one int per thread (1024 threads) */
+__device__ __forceinline__ int scan1024(int v, int *sh) {
+    const int t = threadIdx.x;
+    sh[t] = v;
+    __syncthreads();
+    for (int dlt = 1; dlt < 1024; dlt <<= 1) { const int u = t >= dlt ? sh[t - dlt] : 0; __syncthreads(); sh[t] += u; __syncthreads(); }
+    return sh[t];
 }
-__global__ void k_tc_scan(const int *count, int groups, int *offsets) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int o = 0;
-    for (int g = 0; g < groups; g++) { offsets[g] = o; o += count[g]; }
-    offsets[groups] = o;
+/* activation tiles: each group's rows in the fewest tiles of at most 128 rows, evenly sized. One thread per
+ * group (groups <= 1024) counts its tiles, a scan places them, each thread writes its own. Row ranges are
+ * clamped to [0, max_rows]: offsets come from the caller (or from counts another GPU sent). */
+__global__ void __launch_bounds__(1024) k_tc_plan(const int *offsets, int groups, int fixed_rows, int max_rows, int *tiles, int *n_tiles, int cap) {
+    __shared__ int sh[1024];
+    const int g = threadIdx.x;
+    int first = 0, cnt = 0;
+    if (g < groups) {
+        first = offsets ? offsets[g] : 0;
+        int last = offsets ? offsets[g + 1] : fixed_rows;
+        first = first < 0 ? 0 : (first > max_rows ? max_rows : first);
+        last = last < first ? first : (last > max_rows ? max_rows : last);
+        cnt = last - first;
+    }
+    const int nt = cnt > 0 ? (cnt + kTileN - 1) / kTileN : 0;
+    const int per = nt > 0 ? ((((cnt + nt - 1) / nt) + 15) & ~15) : 0;
+    int mine = 0;
+    for (int i = 0; i < nt; i++) if (cnt - i * per > 0) mine++;
+    const int end = scan1024(mine, sh);
+    int n = end - mine;
+    for (int i = 0; i < mine && n < cap; i++, n++) {
+        const int left = cnt - i * per;
+        tiles[3 * n] = g; tiles[3 * n + 1] = first + i * per; tiles[3 * n + 2] = left < per ? left : per;
+    }
+    if (g == 1023) *n_tiles = end < cap ? end : cap;
+}
+__global__ void __launch_bounds__(1024) k_tc_scan(const int *count, int groups, int *offsets) {
+    __shared__ int sh[1024];
+    const int g = threadIdx.x;
+    const int end = scan1024(g < groups ? count[g] : 0, sh);
+    if (g < groups) offsets[g + 1] = end;
+    if (g == 0) offsets[0] = 0;
 }
 __global__ void __launch_bounds__(256) k_tc_pairs(const int *sel_asc, const int *pairpos, const int *offsets, int n_pairs, int NU, int *gather, int *rowmap) {
     const int p = blockIdx.x * 256 + threadIdx.x;
@@ -396,7 +413,7 @@ cudaError_t sp_tc_shared_expert(SpTcPlan *p, const SpDims &d, const SpLayerDev &
                                 int *status, cudaStream_t st, int *nl) {
     if (!p || M > p->Mcap) return cudaErrorInvalidValue;
     k_tc_split<<<M, 256, 0, st>>>(nx, nullptr, d.E, p->nx_hi, p->nx_lo); (*nl)++;
-    k_tc_plan<<<1, 32, 0, st>>>(nullptr, 1, M, p->tiles_sh, p->ntiles_sh, p->cap_sh); (*nl)++;
+    k_tc_plan<<<1, 1024, 0, st>>>(nullptr, 1, M, M, p->tiles_sh, p->ntiles_sh, p->cap_sh); (*nl)++;
     TcArgs a{};
     a.codes[0] = L.sg_codes; a.bs[0] = L.sg_bs; a.codes[1] = L.su_codes; a.bs[1] = L.su_bs;
     a.group_rows = 0; a.acc1_off = 0; a.rows = d.FFS; a.K = d.E; a.tiles = p->tiles_sh; a.n_tiles = p->ntiles_sh;
@@ -415,7 +432,7 @@ cudaError_t sp_tc_routed(SpTcPlan *p, const SpDims &d, const SpLayerDev &L, int 
     if (!p || R > p->Rcap) return cudaErrorInvalidValue;
     if (R == 0) return cudaSuccess;
     k_tc_split<<<R, 256, 0, st>>>(src, gather, d.E, p->in_hi, p->in_lo); (*nl)++;
-    k_tc_plan<<<1, 32, 0, st>>>(offsets, d.NE, 0, p->tiles_r, p->ntiles_r, p->cap_r); (*nl)++;
+    k_tc_plan<<<1, 1024, 0, st>>>(offsets, d.NE, 0, R, p->tiles_r, p->ntiles_r, p->cap_r); (*nl)++;
     TcArgs a{};
     a.codes[0] = a.codes[1] = L.gu_codes; a.bs[0] = a.bs[1] = L.gu_bs;
     a.group_rows = 2LL * d.FFE; a.acc1_off = d.FFE; a.rows = d.FFE; a.K = d.E; a.tiles = p->tiles_r; a.n_tiles = p->ntiles_r;
@@ -432,7 +449,7 @@ cudaError_t sp_tc_routed(SpTcPlan *p, const SpDims &d, const SpLayerDev &L, int 
 cudaError_t sp_tc_sort_pairs(SpTcPlan *p, const SpDims &d, int M, const int *sel_asc, const int *count, const int *pairpos,
                              const int **offsets, const int **gather, const int **rowmap, cudaStream_t st, int *nl) {
     if (!p || (long long)M * d.NU > p->Rcap) return cudaErrorInvalidValue;
-    k_tc_scan<<<1, 32, 0, st>>>(count, d.NE, p->offsets); (*nl)++;
+    k_tc_scan<<<1, 1024, 0, st>>>(count, d.NE, p->offsets); (*nl)++;
     const int np = M * d.NU;
     k_tc_pairs<<<(np + 255) / 256, 256, 0, st>>>(sel_asc, pairpos, p->offsets, np, d.NU, p->gather, p->rowmap); (*nl)++;
     *offsets = p->offsets; *gather = p->gather; *rowmap = p->rowmap;

@@ -2,7 +2,7 @@
  * operator (CF:13821-13977 of src/backends/cuda/cuda_forward.cu), same signature and semantics:
  * all pointers are host memory; it allocates, uploads the whole packed expert set, runs and frees.
  *
- * Semantics (they differ from the served layer, see decode.cu): ONE weightless rmsnorm with a
+ * Semantics (they differ from the served layer, decode_graph.cu): ONE weightless rmsnorm with a
  * float sum of squares (dg_k_rmsnorm_vec, CF:13632-13644); experts consume that normed vector;
  * router input = normed * (1/sqrt(E) * scale[i]) (CF:13647-13650); logits by a lane-strided
  * fp32 GEMV (dg_k_gemv_f32, CF:13655-13665); host softmax with float expf and a double sum,
@@ -11,6 +11,7 @@
  * dp4a GEMV gate|up, GeGLU, quant, down GEMV, yo += w * de (CF:13930-13958).
  */
 #include "common.cuh"
+#include "gemv_common.cuh"
 #include "../../include/sp_engine/moe_backend.h"
 #include <cmath>
 #include <cstdio>
@@ -42,36 +43,6 @@ __global__ void k_sa_gemv_f32(const float *W, const float *x, float *y, int in, 
     for (int i = lane; i < in; i += 32) acc = __fmaf_rn(wr[i], x[i], acc);
     for (int s = 16; s > 0; s >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, s);
     if (lane == 0) y[o] = acc;
-}
-/* k_quant_act_int8 (CF:1564-1585) into the de-interleaved layout q4b_chunk_dot expects */
-__global__ void k_sa_quant(const float *x, int n, signed char *q, float *sx, int *corr) {
-    for (int b = threadIdx.x; b < (n >> 4); b += blockDim.x) {
-        float v[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = x[16 * b + i];
-        sx[b] = quant_block16(v, q + 16 * b, corr + b);
-    }
-}
-/* k_gemv_q4b_dp4a_v2 (CF:1688-1713): warp per row, chunk c in lane c%32, shuffle tree */
-__global__ void k_sa_gemv_q4b(const uint8_t *codes, const uint16_t *bs, int in, int out,
-                              const signed char *q, const float *sx, const int *corr, float *y) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int j = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (j >= out) return;
-    const int n32 = in >> 5;
-    const uint8_t *row = codes + (size_t)j * (in >> 1);
-    const uint16_t *rbs = bs + (size_t)j * n32;
-    const int4 *q4 = reinterpret_cast<const int4 *>(q);
-    float facc = 0.0f;
-    for (int c = lane; c < n32; c += 32) {
-        const int4 w = ld_stream16(row + 16 * (size_t)c);
-        int a0, a1;
-        q4b_chunk_dot(w, q4[2 * c], q4[2 * c + 1], corr[2 * c], corr[2 * c + 1], a0, a1);
-        const float t = __fmaf_rn((float)a0, sx[2 * c], __fmul_rn((float)a1, sx[2 * c + 1]));
-        facc = __fmaf_rn(h2f(rbs[c]), t, facc);
-    }
-    for (int o = 16; o > 0; o >>= 1) facc += __shfl_down_sync(0xffffffffu, facc, o);
-    if (lane == 0) y[j] = facc;
 }
 __global__ void k_sa_geglu(const float *gu, float *h, int FF) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -145,12 +116,12 @@ extern "C" int gemma4_moe_ffn_q4b_cuda(int E, int NE, int NU, int FF, float eps,
     SA(cudaMemsetAsync(d_yo, 0, (size_t)E * 4, st), "memset");
     for (int k = 0; k < NU; k++) {
         const int e = idx[k];
-        k_sa_quant<<<1, 256, 0, st>>>(d_x, E, d_q, d_sx, d_corr);
-        k_sa_gemv_q4b<<<(unsigned)((gu_rows + 7) / 8), 256, 0, st>>>(d_gc + (size_t)e * gu_rows * (E / 2), d_gs + (size_t)e * gu_rows * (E / 32),
+        k_quant_act<<<1, 256, 0, st>>>(d_x, E, d_q, d_sx, d_corr);
+        k_gemv_q4b<<<(unsigned)((gu_rows + 7) / 8), 256, 0, st>>>(d_gc + (size_t)e * gu_rows * (E / 2), d_gs + (size_t)e * gu_rows * (E / 32),
                                                                   E, (int)gu_rows, d_q, d_sx, d_corr, d_gu);
         k_sa_geglu<<<(FF + 255) / 256, 256, 0, st>>>(d_gu, d_h, FF);
-        k_sa_quant<<<1, 256, 0, st>>>(d_h, FF, d_q, d_sx, d_corr);
-        k_sa_gemv_q4b<<<(unsigned)((dn_rows + 7) / 8), 256, 0, st>>>(d_dc + (size_t)e * dn_rows * (FF / 2), d_ds + (size_t)e * dn_rows * (FF / 32),
+        k_quant_act<<<1, 256, 0, st>>>(d_h, FF, d_q, d_sx, d_corr);
+        k_gemv_q4b<<<(unsigned)((dn_rows + 7) / 8), 256, 0, st>>>(d_dc + (size_t)e * dn_rows * (FF / 2), d_ds + (size_t)e * dn_rows * (FF / 32),
                                                                   FF, (int)dn_rows, d_q, d_sx, d_corr, d_de);
         k_sa_axpy<<<(E + 255) / 256, 256, 0, st>>>(d_yo, d_de, wt[k], E);
     }
@@ -175,8 +146,8 @@ extern "C" int sp_moe_gemv_q4b_dev(const uint8_t *codes_dev, const uint16_t *bs_
     if (e == cudaSuccess) e = cudaMalloc(&sx, sizeof(float) * (in / 16));
     if (e == cudaSuccess) e = cudaMalloc(&corr, sizeof(int) * (in / 16));
     if (e == cudaSuccess) {
-        k_sa_quant<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
-        k_sa_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
+        k_quant_act<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
+        k_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
         e = cudaGetLastError();
         if (e == cudaSuccess) e = cudaStreamSynchronize(st);            /* the scratch is freed below */
     }
@@ -231,8 +202,8 @@ extern "C" int sp_moe_gemv_q4b_static_dev(const uint8_t *codes_dev, const uint16
         float *sx = reinterpret_cast<float *>(base + SP_MOE_GEMV_STATIC_MAX_IN);
         int *corr = reinterpret_cast<int *>(base + SP_MOE_GEMV_STATIC_MAX_IN + 4 * (SP_MOE_GEMV_STATIC_MAX_IN / 16));
         /* nothing in the scratch has to start at zero: the quantiser writes every byte the GEMV reads */
-        k_sa_quant<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
-        k_sa_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
+        k_quant_act<<<1, 256, 0, st>>>(x_dev, in, q, sx, corr);
+        k_gemv_q4b<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(codes_dev, bs_dev, in, rows, q, sx, corr, y_dev);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) { char b[256]; snprintf(b, sizeof b, "sp_moe_gemv_q4b_static_dev: %s", cudaGetErrorString(e)); sp_set_error(b); cudaGetLastError(); return SP_MOE_ECUDA; }

@@ -117,6 +117,22 @@ class MoeEngine:
     def status(self):
         check(_lib.lib().sp_moe_status(self._h))
 
+    def decode_timing(self):
+        """Phase times (microseconds, device clock, CTA 0) of the last layer of the most recent single-token
+        decode call; needs SP_MOE_TIMING=1 in the environment when the engine was created (the reference's
+        switch for its `[g4-moe] TIMING` line, src/backends/cuda/cuda_forward.cu:7186-7201)."""
+        t = _lib.SpMoeTiming()
+        check(_lib.lib().sp_moe_decode_timing(self._h, C.byref(t)))
+        names = ("router+shared", "topk+gate|up", "down+combine")
+        return dict(layer_us=t.layer_us, raw_us=[[round(v, 3) for v in row] for row in t.raw_us], kernels={n: dict(wait_us=t.wait_us[k], prologue_us=t.prologue_us[k], rows_us=t.rows_us[k])
+                                                   for k, n in enumerate(names)})
+
+    def debug_wait_timeout(self, polls=4096):
+        """Failure-path probe: a one-CTA kernel waits (at most `polls` polls) on a copy nobody starts; the
+        wait gives up and the next status() raises the library's timeout error. Nothing hangs."""
+        import torch
+        check(_lib.lib().sp_moe_debug_wait_timeout(self._h, polls, torch.cuda.current_stream().cuda_stream))
+
     # -- one layer in three stages (expert-parallel runs move rows between them; see ep.py)
     def ep_route(self, layer, x, flavour=FLAVOUR_PREFILL, sel=None, wts=None, defer_shared=False, n_ranks=0, capacity=0):
         """x torch CUDA f32 [M][E] -> (sel_asc int32 [M][NU], cw f32 [M][NU], rows f32 sorted by expert,

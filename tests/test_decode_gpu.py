@@ -114,3 +114,102 @@ def test_gemv_q4b_entry_matches_checker_bitwise():
         qx, sx = orc.quant_act(x.cpu().numpy())
         ref = orc.gemv_a(codes.cpu().numpy(), bs.cpu().numpy().view(np.uint16), rows, cols, qx, sx)
         assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("cfg,n_layers", [(orc.SMALL, 4), (orc.GEMMA, 2)])
+def test_decode_direct_rows_path(cfg, n_layers, monkeypatch):
+    """SP_MOE_DECODE_IMPL=direct: the kernels that read weight rows straight from global memory (the
+    path for geometries whose per-CTA slices do not fit shared memory). Same checker, and bit-identical
+    to the default path that stages rows through shared memory."""
+    x = np.random.default_rng(23).standard_normal((1, cfg["E"])).astype(np.float32)
+    monkeypatch.setenv("SP_MOE_DECODE_IMPL", "direct")
+    eng, host = make_stack(cfg, n_layers, seed=13, rand_norms=True)
+    monkeypatch.delenv("SP_MOE_DECODE_IMPL")
+    y, sel, wts = eng.forward(x)
+    eng.close()
+    ry, rsel, rwts, margin = oracle_stack(cfg, host, x, 0)
+    assert np.array_equal(sel, rsel), f"expert ids differ (min margin {margin:.3e})"
+    assert_close(y, ry, "direct rows path")
+    eng2, _ = make_stack(cfg, n_layers, seed=13, rand_norms=True)
+    y2, sel2, wts2 = eng2.forward(x)
+    eng2.close()
+    assert np.array_equal(sel2, sel) and np.array_equal(wts2.view(np.uint32), wts.view(np.uint32))
+    assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_survivable():
+    """A device-side wait that can never be satisfied gives up after its poll limit, the kernel returns,
+    and the host reads the timeout through the status call; the handle keeps working."""
+    from kairos_engine_b200 import SpMoeError
+    cfg = orc.TINY
+    eng, host = make_stack(cfg, 1, seed=3)
+    eng.debug_wait_timeout(polls=2000)
+    with pytest.raises(SpMoeError) as ei:
+        eng.status()
+    assert ei.value.code == -40 and "bounded device-side wait ran out" in ei.value.text
+    eng.status()                                       # the error word was cleared
+    x = np.random.default_rng(2).standard_normal((1, cfg["E"])).astype(np.float32)
+    y, sel, _ = eng.forward(x)
+    ry, rsel, _, _ = oracle_stack(cfg, host, x, 0)
+    assert np.array_equal(sel, rsel)
+    assert_close(y, ry, "after a timed-out wait")
+    eng.close()
+
+
+def test_decode_phase_timing_entry(monkeypatch):
+    from kairos_engine_b200 import SpMoeError
+    cfg = orc.SMALL
+    eng, _ = make_stack(cfg, 2, seed=4)
+    with pytest.raises(SpMoeError):                    # not switched on: no clock is read, the call says so
+        eng.decode_timing()
+    eng.close()
+    monkeypatch.setenv("SP_MOE_TIMING", "1")
+    eng, _ = make_stack(cfg, 2, seed=4)
+    monkeypatch.delenv("SP_MOE_TIMING")
+    x = np.random.default_rng(2).standard_normal((1, cfg["E"])).astype(np.float32)
+    eng.forward(x)
+    t = eng.decode_timing()
+    assert 0.0 < t["layer_us"] < 1e4
+    for k in t["kernels"].values():
+        assert k["wait_us"] >= 0.0 and k["prologue_us"] > 0.0 and k["rows_us"] >= 0.0
+    eng.close()
+
+
+def test_reupload_with_and_without_bias_drops_the_captured_graph():
+    """A captured decode graph holds the layer's view by value; uploading the layer again with a router
+    bias it lacked (or without one it had) must take effect on the next call."""
+    import torch
+    from kairos_engine_b200 import MoeEngine, synth
+    cfg = orc.SMALL
+    eng = MoeEngine(n_layers=1, **cfg)
+    layer = synth.make_layer(cfg, 5)
+    eng.upload_layer(0, layer, on_device=True)
+    x = np.random.default_rng(8).standard_normal((1, cfg["E"])).astype(np.float32)
+    y0, sel0, _ = eng.forward(x)
+    biased = dict(layer); biased["router_bias"] = synth.zipf_bias(cfg["NE"], s=2.0, seed=1) * 8.0
+    eng.upload_layer(0, biased, on_device=True)
+    y1, sel1, _ = eng.forward(x)
+    ref = orc.layer_forward(cfg, orc.LayerWeights(**synth.layer_to_host(biased)), x, 0)
+    assert np.array_equal(sel1[0], ref["sel"]) and not np.array_equal(sel1, sel0)
+    eng.upload_layer(0, layer, on_device=True)
+    y2, sel2, _ = eng.forward(x)
+    assert np.array_equal(sel2, sel0) and np.array_equal(y2.view(np.uint32), y0.view(np.uint32))
+    eng.close()
+
+
+def test_handles_on_two_devices_in_one_process():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from kairos_engine_b200 import MoeEngine, synth
+    cfg = orc.SMALL
+    x = np.random.default_rng(3).standard_normal((1, cfg["E"])).astype(np.float32)
+    outs = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            eng = MoeEngine(n_layers=2, device=dev, **cfg)
+            for L in range(2):
+                eng.upload_layer(L, synth.make_layer(cfg, 30 + L, device=f"cuda:{dev}"), on_device=True)
+            outs.append(eng.forward(x)[0])
+            eng.close()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))

@@ -123,6 +123,44 @@ def test_receive_layout_kernel_matches_host_arithmetic():
     eng.close()
 
 
+def test_receive_layout_stays_inside_the_buffer_when_a_source_overflows():
+    """A source whose block for this rank overflowed reports its full counts but delivered only
+    `capacity` rows (the first ones, in expert order). The layout must follow what was delivered:
+    no arrival row outside the receive buffer, no more sorted rows than the buffer holds, and the
+    experts stage must run on it without touching anything else."""
+    import torch
+    cfg = orc.SMALL                                                  # 16 experts
+    world, C = 4, 12
+    eng, _ = make_stack(cfg, 1, seed=37, max_tokens=64, max_expert_rows=world * C)
+    epr = cfg["NE"] // world
+    counts_all = torch.full((world, cfg["NE"]), 2, dtype=torch.int32)      # 8 rows per source and rank: fits
+    counts_all[world - 1, :] = 7                                           # the LAST source sends 28 > 12 to every rank
+    counts_all[1, 0] = 30                                                  # and one expert alone exceeds the capacity
+    for rank in range(world):
+        off, idx = eng.ep_recv_layout(counts_all.cuda(), rank, C)
+        off, idx = off.cpu(), idx.cpu()
+        kept = torch.zeros(world, epr, dtype=torch.int64)
+        for s in range(world):
+            room = C
+            for e in range(epr):
+                kept[s, e] = min(int(counts_all[s, rank * epr + e]), room); room -= int(kept[s, e])
+        total = int(kept.sum())
+        assert int(off[cfg["NE"]]) == total <= world * C
+        assert off[rank * epr:(rank + 1) * epr + 1].tolist() == [0] + torch.cumsum(kept.sum(0), 0).tolist()
+        assert int(idx.min()) >= 0 and int(idx.max()) < world * C
+        want = []
+        for e in range(epr):
+            for s in range(world):
+                start = s * C + int(kept[s, :e].sum())
+                want += list(range(start, start + int(kept[s, e])))
+        assert idx[:total].tolist() == want
+        rows = torch.randn(world * C, cfg["E"], device="cuda")
+        out = eng.ep_experts(0, rows, off.cuda(), flavour=B, row_index=idx.cuda())
+        eng.status()
+        assert torch.isfinite(out[idx[:total].long().cuda()]).all()
+    eng.close()
+
+
 def test_padded_route_reports_a_block_that_does_not_fit():
     import torch
     from kairos_engine_b200 import SpMoeError

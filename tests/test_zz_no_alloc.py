@@ -12,6 +12,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import orc
+
 pytestmark = pytest.mark.gpu
 
 
@@ -39,6 +41,10 @@ def test_static_scratch_gemv_matches_allocating_entry_twice_in_a_row():
         assert rc_ref == 0 and rc_new == 0, L.sp_last_error()
         # same kernels, same arithmetic: the tolerance the other GEMV tests use is bit equality
         assert np.array_equal(y_new.view(np.uint32), y_ref.view(np.uint32))
+        # and directly against the CPU checker (itself pinned to the reference's sp_moe_cpu_gemv)
+        qx, sx = orc.quant_act(x.cpu().numpy())
+        ref = orc.gemv_a(codes.cpu().numpy(), bs.cpu().numpy().view(np.uint16), rows, cols, qx, sx)
+        assert np.array_equal(y_new.view(np.uint32), ref.view(np.uint32))
 
 
 def test_static_scratch_gemv_refuses_sizes_beyond_its_array():
