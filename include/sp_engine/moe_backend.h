@@ -241,7 +241,7 @@ typedef struct {
     float prologue_us[3];  /* -> activations normalised / selected / quantised in shared memory */
     float rows_us[3];      /* -> last weight row of the CTA's slice done */
     float layer_us;        /* first kernel's entry -> last kernel's last row */
-    float raw_us[3][8];    /* every stamp a kernel took, microseconds since the first kernel's entry (0 = not taken) */
+    float raw_us[3][16];   /* every stamp a kernel took, microseconds since the first kernel's entry (0 = not taken) */
 } sp_moe_timing;
 int sp_moe_decode_timing(sp_moe *h, sp_moe_timing *out);
 

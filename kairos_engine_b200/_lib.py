@@ -36,7 +36,7 @@ class SpMoeLayerWeights(C.Structure):
 
 class SpMoeTiming(C.Structure):
     _fields_ = [("wait_us", C.c_float * 3), ("prologue_us", C.c_float * 3), ("rows_us", C.c_float * 3),
-                ("layer_us", C.c_float), ("raw_us", (C.c_float * 8) * 3)]
+                ("layer_us", C.c_float), ("raw_us", (C.c_float * 16) * 3)]
 
 
 class SpMoeError(RuntimeError):

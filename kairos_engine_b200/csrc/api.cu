@@ -161,8 +161,16 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
                      o_q = take(E), o_s = take(4 * (E / 16)), o_c = take(4 * (E / 16)), o_sel = take(4 * SP_MAX_NU), o_cw = take(4 * SP_MAX_NU),
                      o_x0 = take(4 * E), o_x1 = take(4 * E), o_gx = take(4 * E), o_gy = take(4 * E),
                      o_gsel = take(4 * NU * (size_t)c.n_layers), o_gw = take(4 * NU * (size_t)c.n_layers);
+        cudaDeviceGetAttribute(&h->sms, cudaDevAttrMultiProcessorCount, c.device);
+        const size_t o_sl = take(48 * (size_t)h->sms);
         OPEN_CK(dalloc((void **)&h->gs_base, o), "scratch");
         unsigned char *b = h->gs_base;
+        {
+            std::vector<int> sl(12 * (size_t)h->sms);
+            sp_staged_slices(h->d, h->sms, sl.data());
+            OPEN_CK(cudaMemcpy(b + o_sl, sl.data(), sl.size() * sizeof(int), cudaMemcpyHostToDevice), "slice table H2D");
+            h->gs.slices = (const int *)(b + o_sl);
+        }
         h->gs.logits = (float *)(b + o_lg); h->gs.hd = (float *)(b + o_hd); h->gs.dn = (float *)(b + o_dn); h->gs.h = (float *)(b + o_h); h->gs.acc = (float *)(b + o_acc);
         h->gs.in_q = (signed char *)(b + o_q); h->gs.in_s = (float *)(b + o_s); h->gs.in_c = (int *)(b + o_c);
         h->gs.sel_asc = (int *)(b + o_sel); h->gs.cw = (float *)(b + o_cw); h->gs.status = h->status;
@@ -183,9 +191,9 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         if (h->decode_impl == 0) OPEN_CK(sp_staged_prepare(h->d, h->sms), "decode kernel attributes");
         const char *tv = getenv("SP_MOE_TIMING");                 /* the reference's switch for its [g4-moe] TIMING line (CF:7186-7201) */
         if (tv && tv[0] == '1') {
-            OPEN_CK(dalloc((void **)&h->stamps, 24 * sizeof(long long)), "timing stamps");
-            OPEN_CK(cudaMemset(h->stamps, 0, 24 * sizeof(long long)), "memset");
-            OPEN_CK(cudaMallocHost((void **)&h->stamps_host, 24 * sizeof(long long)), "timing stamps (host)");
+            OPEN_CK(dalloc((void **)&h->stamps, 48 * sizeof(long long)), "timing stamps");
+            OPEN_CK(cudaMemset(h->stamps, 0, 48 * sizeof(long long)), "memset");
+            OPEN_CK(cudaMallocHost((void **)&h->stamps_host, 48 * sizeof(long long)), "timing stamps (host)");
         }
     }
     { size_t bb = 0; cudaError_t be = sp_batched_alloc(h->d, c.max_tokens, c.max_expert_rows, &h->bs, &bb); sb += bb; OPEN_CK(be, "batched scratch"); }
@@ -434,16 +442,16 @@ extern "C" int sp_moe_status(sp_moe *h) {
 
 /* ---------------------------------------------------------------- phase timing (SP_MOE_TIMING=1) */
 static int read_timing(sp_moe *h, sp_moe_timing *t) {
-    CK(cudaMemcpyAsync(h->stamps_host, h->stamps, 24 * sizeof(long long), cudaMemcpyDeviceToHost, h->last_stream), "timing D2H");
+    CK(cudaMemcpyAsync(h->stamps_host, h->stamps, 48 * sizeof(long long), cudaMemcpyDeviceToHost, h->last_stream), "timing D2H");
     CK(cudaStreamSynchronize(h->last_stream), "stream synchronize");
     const long long *s = h->stamps_host;
     for (int k = 0; k < 3; k++) {
-        t->wait_us[k] = (float)((s[k * 8 + 1] - s[k * 8 + 0]) * 1e-3);
-        t->prologue_us[k] = (float)((s[k * 8 + 3] - s[k * 8 + 1]) * 1e-3);
-        t->rows_us[k] = (float)((s[k * 8 + 4] - s[k * 8 + 3]) * 1e-3);
+        t->wait_us[k] = (float)((s[k * 16 + 1] - s[k * 16 + 0]) * 1e-3);
+        t->prologue_us[k] = (float)((s[k * 16 + 3] - s[k * 16 + 1]) * 1e-3);
+        t->rows_us[k] = (float)((s[k * 16 + 4] - s[k * 16 + 3]) * 1e-3);
     }
-    t->layer_us = (float)((s[2 * 8 + 4] - s[0]) * 1e-3);
-    for (int k = 0; k < 3; k++) for (int i = 0; i < 8; i++) t->raw_us[k][i] = s[k * 8 + i] ? (float)((s[k * 8 + i] - s[0]) * 1e-3) : 0.0f;
+    t->layer_us = (float)((s[2 * 16 + 4] - s[0]) * 1e-3);
+    for (int k = 0; k < 3; k++) for (int i = 0; i < 16; i++) t->raw_us[k][i] = s[k * 16 + i] ? (float)((s[k * 16 + i] - s[0]) * 1e-3) : 0.0f;
     return SP_MOE_OK;
 }
 extern "C" int sp_moe_decode_timing(sp_moe *h, sp_moe_timing *out) {

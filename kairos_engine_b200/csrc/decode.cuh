@@ -11,6 +11,7 @@ struct SpGraphScratch {
     int *status;
     float *xbuf[2];                             /* residual between layers, ping-pong */
     const float *prev_post_ffw1, *prev_post_ffw2, *prev_post_ffw;   /* set per launch */
+    const int *slices;                          /* [grid][12]: each CTA's share of every phase (sp_staged_slices) */
 };
 
 /* ---- decode_graph.cu ---- */
@@ -32,8 +33,9 @@ enum {
 /* true when one CTA's slice of every phase fits `smem_optin` bytes of shared memory on a grid of `sms` CTAs */
 bool sp_staged_fits(const SpDims &d, int sms, size_t smem_optin);
 cudaError_t sp_staged_prepare(const SpDims &d, int sms);
-/* stamps: NULL, or 24 device words that receive CTA 0's globaltimer readings in the last layer of the run:
- * [kernel 0..2][0 entry, 1 predecessor done, 2 mid-prologue, 3 prologue done, 4 rows done] */
+void sp_staged_slices(const SpDims &d, int sms, int *out /* [sms][12] */);
+/* stamps: NULL, or 48 device words that receive CTA 0's globaltimer readings in the last layer of the run:
+ * [kernel 0..2][16]: 0 entry, 1 predecessor done, 2 activations ready, 3 first weight row may start, 4 rows done, 5.. finer marks */
 cudaError_t sp_staged_decode_enqueue(const SpDims &d, const SpLayerDev *layers_host, int lf, int nl, const float *x_in, float *y_out,
                                      int32_t *sel, float *wts, const SpGraphScratch &sc, int sms, unsigned flags, long long *stamps,
                                      cudaStream_t st, bool pdl, int *nlaunch);
