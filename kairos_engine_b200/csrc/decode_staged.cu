@@ -698,13 +698,11 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_up(SArgs a) {
                 if (i < nP) {                             /* warp-uniform */
                     bar_wait(smem_u32(&ctl->bar[1]), &ctl->abort, a.s.status);              /* the scale rows travel with part 0 */
                     bar_wait(smem_u32(&ctl->bar[1 + (i >> LP)]), &ctl->abort, a.s.status);
-                    if (i == 0) STAMP(1, 8); else if (i == kW) STAMP(1, 10);
                     const int run = i >= n0, idx = run ? i - n0 : i;
                     RowW<NIT_E> wg, wu;
                     row_fetch<NIT_E>(wg, sm + ly.st_gc + (unsigned)i * rbE, sm + ctl->gs_off[run] + (unsigned)idx * sbE, n32, lane);
                     row_fetch<NIT_E>(wu, sm + ly.st_uc + (unsigned)i * rbE, sm + ctl->us_off[run] + (unsigned)idx * sbE, n32, lane);
                     f[2 * k] = row_dot<NIT_E>(wg, act); f[2 * k + 1] = row_dot<NIT_E>(wu, act);
-                    if (i == 0) STAMP(1, 9); else if (i == kW) STAMP(1, 11);
                 }
             }
             const float tot = tree8(f, lane);             /* lane 4r (and its three neighbours) holds row r: gate of pair k in lanes 8k.., up in lanes 8k+4.. */
@@ -722,12 +720,6 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_up(SArgs a) {
         }
     }
     STAMP(1, 12);
-    if (a.stamps && blockIdx.x == 0) {
-        __shared__ long long wt_[32];
-        if (lane == 0) { long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); wt_[warp] = t_; }
-        __syncthreads();
-        if (t == 0) { long long m = 0; int am = 0; for (int w = 0; w < kW; w++) if (wt_[w] > m) { m = wt_[w]; am = w; } a.stamps[16 + 13] = m; a.stamps[16 + 14] = a.stamps[0] + 1000 * am; a.stamps[16 + 15] = wt_[kW - 1]; }
-    }
     __syncthreads();
     STAMP(1, 4);
 }
@@ -849,7 +841,7 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
     for (int bq = t + kT; bq < nblk; bq += kT) quant_from_global(a.s.h + 16 * bq, reinterpret_cast<int4 *>(q_h) + bq, s_h + bq, c_h + bq);
     STAMP(2, 6);
     __syncthreads();
-    STAMP(2, 2);
+    STAMP(2, 3);
     if ((a.flags & SP_STAGED_PREFETCH_NEXT) && a.has_next) {   /* the next layer's router rows and shared gate/up pairs of this CTA's slice */
         const SpLayerDev &N = a.Ln;
         const int r0 = sl0.x, nr = sl0.y, p0 = sl0.z, np = sl0.w;
@@ -865,13 +857,13 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
         ActR<NIT> act; int act_slot = -1;
         if (NIT == 1) {                                   /* eight rows per round while a row is one chunk per lane (registers) */
 #pragma unroll 1
-            for (; u + 8 <= ub; u += 8) down_round<NIT, NIT == 1 ? 8 : 2>(sm, ly, ctl, a.s.status, s, jj, 8, nj, njm, SGs, rb, sb, n32, blk16, lane, out, act, act_slot);
+            for (; ub - u >= 5; u += 8) down_round<NIT, NIT == 1 ? 8 : 2>(sm, ly, ctl, a.s.status, s, jj, ub - u < 8 ? ub - u : 8, nj, njm, SGs, rb, sb, n32, blk16, lane, out, act, act_slot);
         }
 #pragma unroll 1
         for (; u < ub; u += 2) down_round<NIT, 2>(sm, ly, ctl, a.s.status, s, jj, ub - u < 2 ? ub - u : 2, nj, njm, SGs, rb, sb, n32, blk16, lane, out, act, act_slot);
     }
     __syncthreads();
-    STAMP(2, 3);
+    STAMP(2, 7);
 #pragma unroll 1
     for (int jj = t; jj < nj; jj += kT) {                 /* k_moe_combine_ord, CF:6071-6077 */
         float o[SP_MAX_NU], w[SP_MAX_NU];
