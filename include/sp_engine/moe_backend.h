@@ -88,6 +88,11 @@ int  sp_moe_close(sp_moe *h);
  * are HOST memory in sp_moe_upload_layer and DEVICE memory in sp_moe_upload_layer_dev. */
 int  sp_moe_upload_layer(sp_moe *h, int layer, const sp_moe_layer_weights *w);
 int  sp_moe_upload_layer_dev(sp_moe *h, int layer, const sp_moe_layer_weights *w);
+/* Replaces only the router's per-expert logit bias of one layer (DEVICE pointer to NE floats, or NULL for
+ * no bias); the other tensors stay as uploaded. The reference adds such a bias where the model file carries
+ * one (`ffn_gate_inp.bias`, read with the router in build_weights, CF:2258-2268); load-imbalance experiments
+ * use it to skew the routing without touching the experts. */
+int  sp_moe_set_router_bias_dev(sp_moe *h, int layer, const float *bias_dev);
 /* Bytes of device memory the handle holds (arena + scratch). */
 size_t sp_moe_device_bytes(const sp_moe *h);
 

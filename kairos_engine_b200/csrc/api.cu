@@ -224,6 +224,7 @@ extern "C" int sp_moe_close(sp_moe *h) {
 extern "C" size_t sp_moe_device_bytes(const sp_moe *h) { return h ? h->arena_bytes + h->scratch_bytes : 0; }
 extern "C" uint64_t sp_moe_kernel_launches(const sp_moe *h) { return h ? h->launches : 0; }
 
+static void drop_graphs_of_layer(sp_moe *h, int L);
 static int upload(sp_moe *h, int L, const sp_moe_layer_weights *w, cudaMemcpyKind kind, const char *who) {
     if (!h || !w) return fail(SP_MOE_EBADARG, "%s: NULL argument", who);
     if (L < 0 || L >= h->cfg.n_layers) return fail(SP_MOE_EBADARG, "%s: layer %d out of range [0, %d)", who, L, h->cfg.n_layers);
@@ -247,13 +248,29 @@ static int upload(sp_moe *h, int L, const sp_moe_layer_weights *w, cudaMemcpyKin
 #undef UP
     h->has_bias[L] = w->router_bias != nullptr;
     h->layers_host[L] = layer_view(h, L, h->has_bias[L]);
+    drop_graphs_of_layer(h, L);
+    CK(cudaMemcpy(h->layers_dev + L, &h->layers_host[L], sizeof(SpLayerDev), cudaMemcpyHostToDevice), who);
+    h->uploaded[L] = 1;
+    return SP_MOE_OK;
+}
+static void drop_graphs_of_layer(sp_moe *h, int L) {
     /* captured graphs hold this layer's view by value (the bias pointer may just have appeared or gone) */
     for (size_t i = h->graphs.size(); i-- > 0;)
         if (L >= h->graphs[i].lf && L < h->graphs[i].lf + h->graphs[i].nl) { cudaGraphExecDestroy(h->graphs[i].exec); h->graphs.erase(h->graphs.begin() + (long)i); }
     for (size_t i = h->bgraphs.size(); i-- > 0;)
         if (L >= h->bgraphs[i].lf && L < h->bgraphs[i].lf + h->bgraphs[i].nl) { cudaGraphExecDestroy(h->bgraphs[i].exec); h->bgraphs.erase(h->bgraphs.begin() + (long)i); }
-    CK(cudaMemcpy(h->layers_dev + L, &h->layers_host[L], sizeof(SpLayerDev), cudaMemcpyHostToDevice), who);
-    h->uploaded[L] = 1;
+}
+extern "C" int sp_moe_set_router_bias_dev(sp_moe *h, int L, const float *bias_dev) {
+    if (!h) return fail(SP_MOE_EBADARG, "sp_moe_set_router_bias_dev: NULL handle");
+    if (L < 0 || L >= h->cfg.n_layers) return fail(SP_MOE_EBADARG, "sp_moe_set_router_bias_dev: layer %d out of range [0, %d)", L, h->cfg.n_layers);
+    if (!h->uploaded[L]) return fail(SP_MOE_EBADSTATE, "sp_moe_set_router_bias_dev: layer %d has no weights uploaded", L);
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    CK(cudaStreamSynchronize(h->last_stream), "stream synchronize");
+    if (bias_dev) CK(cudaMemcpy(h->arena + (size_t)L * h->layer_bytes + h->off.router_bias, bias_dev, 4 * (size_t)h->cfg.NE, cudaMemcpyDeviceToDevice), "router bias copy");
+    h->has_bias[L] = bias_dev != nullptr;
+    h->layers_host[L] = layer_view(h, L, h->has_bias[L]);
+    CK(cudaMemcpy(h->layers_dev + L, &h->layers_host[L], sizeof(SpLayerDev), cudaMemcpyHostToDevice), "layer table H2D");
+    drop_graphs_of_layer(h, L);
     return SP_MOE_OK;
 }
 extern "C" int sp_moe_upload_layer(sp_moe *h, int L, const sp_moe_layer_weights *w) { return upload(h, L, w, cudaMemcpyHostToDevice, "sp_moe_upload_layer"); }

@@ -76,6 +76,10 @@ class MoeEngine:
         fn = _lib.lib().sp_moe_upload_layer_dev if on_device else _lib.lib().sp_moe_upload_layer
         check(fn(self._h, layer, C.byref(w)))
 
+    def set_router_bias(self, layer, bias):
+        """Replaces the router's per-expert logit bias of one layer (torch CUDA f32 [NE], or None for no bias)."""
+        check(_lib.lib().sp_moe_set_router_bias_dev(self._h, layer, _ptr(bias)))
+
     # -- forward
     def forward(self, x, layer_first=0, n_layers=None, flavour=FLAVOUR_DECODE, want_routing=True, out=None):
         """Host entry: x numpy [M][E] f32 -> (y, sel, wts); sel/wts are [n_layers][M][NU]. `out`: a caller-owned

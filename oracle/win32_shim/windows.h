@@ -3,7 +3,8 @@
  * TEST INFRASTRUCTURE ONLY: used by oracle/Makefile to build oracle/_ref; never by the product.
  * Provides exactly the names that file uses: integer/handle typedefs, __declspec(align(n)),
  * __forceinline, SRWLOCK, Interlocked*, WaitOnAddress/WakeByAddressAll, CreateThread,
- * SetThreadPriority. */
+ * SetThreadPriority; and for tools/moe_cpu_bench/moe_cpu_bench.cu (oracle/ref_gpu_kernels.cu):
+ * GetCurrentThread, SetThreadAffinityMask. */
 #ifndef SP_ORACLE_WIN32_SHIM_H
 #define SP_ORACLE_WIN32_SHIM_H
 #include <stdint.h>
@@ -50,4 +51,6 @@ static inline HANDLE CreateThread(void *sa, size_t ss, LPTHREAD_START_ROUTINE f,
     return t;
 }
 static inline int SetThreadPriority(HANDLE h, int p) { (void)h; (void)p; return 1; }
+static inline HANDLE GetCurrentThread(void) { return 0; }
+static inline unsigned long long SetThreadAffinityMask(HANDLE h, unsigned long long m) { (void)h; return m; }
 #endif

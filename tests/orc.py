@@ -38,10 +38,13 @@ class OrcLayer(C.Structure):
 
 
 def build_oracle(with_ref=True):
-    """Compile the checker (and, where the reference tree is mounted, the reference's own file)."""
+    """Compile the checker and, where the reference tree is mounted (SP_REFERENCE_ROOT, or the Makefile's
+    default), the reference's own CPU expert file and its own decode kernels; without the tree those two
+    targets have no source and are skipped (the prebuilt files under oracle/_ref are then used as they are)."""
     subprocess.run(["make", "-s", "-C", ORACLE_DIR], check=True)
-    if with_ref and os.path.exists("/root/reference/src/backends/cuda/moe_cpu_expert.c"):
-        subprocess.run(["make", "-s", "-C", ORACLE_DIR, "ref"], check=True)
+    if with_ref:
+        for target in ("ref", "ref_gpu"):
+            subprocess.run(["make", "-s", "-C", ORACLE_DIR, target], check=False, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
 
 
 _lib = None
@@ -236,7 +239,7 @@ def standalone_q4b(E, NE, NU, FF, eps, gate_inp, gate_inp_scale, gu_codes, gu_bs
 
 # ---------------------------------------------------------------- seeded synthetic layers (CPU, small)
 def make_layer(cfg, seed, wstd=0.02, rand_norms=False, bias=None):
-    """BASELINE config[0] recipe: router N(0,0.02) f32; expert/shared weights N(0,0.02) then Q4B;
+    """The benchmark's weight recipe: router N(0,0.02) f32; expert/shared weights N(0,0.02) then Q4B;
     scales and norm weights 1 (or uniform [0.5,1.5] when rand_norms)."""
     E, NE, FFE, FFS = cfg["E"], cfg["NE"], cfg["FFE"], cfg["FFS"]
     r = np.random.default_rng(seed)

@@ -41,7 +41,7 @@ def stack30():
 
 
 def test_decode_30_layers_m1_bit_identical(stack30):
-    """BASELINE configs[1]: the full stack, single-token steps. The decode arithmetic re-quantises to
+    """The benchmark's headline configuration: the full stack, single-token steps. The decode arithmetic re-quantises to
     int8 in every layer, so one wrong bit early is a different token later: ids must match at every
     layer and the final hidden state bit for bit."""
     eng, host = stack30
@@ -60,7 +60,7 @@ def test_decode_30_layers_m1_bit_identical(stack30):
 
 
 def test_decode_30_layers_m64_rows_equal_single_token_steps(stack30):
-    """BASELINE configs[2], largest shape: 64 tokens per step through the 30 layers in the decode
+    """The batched-decode / draft-verify configuration, largest shape: 64 tokens per step through the 30 layers in the decode
     arithmetic. Every row must equal, bit for bit, what the single-token kernels give for that token
     (the reference runs a batch as sequential steps, CF:11737-11757); the checker pins 4 of them."""
     eng, host = stack30
@@ -82,7 +82,7 @@ def test_decode_30_layers_m64_rows_equal_single_token_steps(stack30):
 
 
 def test_prefill_4096_tokens_gemma_geometry_sampled_rows():
-    """BASELINE configs[3] on one layer: 4096 tokens through the token-permute + grouped tensor-core
+    """The prefill configuration on one layer: 4096 tokens through the token-permute + grouped tensor-core
     GEMMs. Checked rows: the first and the last token, and for EVERY expert the routed token with
     the highest index and one from the middle of its list (with ~256 rows per expert these sit in
     the expert's second activation tile, which small tests never reach)."""
