@@ -341,11 +341,16 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier, zipf=
     Ml = PT // world
     xp = synth.make_inputs(CFG, Ml, seed=99 + rank, device=f"cuda:{local_rank}")
     yp = torch.empty_like(xp)
-    # N > 1: padded exchange (no host read per layer) with room for 1.25x the average rows per destination
+    # N > 1: padded exchange (no host read per layer) with room for 1.3x the average rows per destination
     # (unbiased routing spreads within a few percent; an overflow on any rank sends all ranks to the exact
     # exchange); the load-imbalance stress uses the exact exchange
-    cap = 0 if (world < 2 or zipf) else -(-5 * Ml * CFG["NU"] // (4 * world) // 8) * 8
-    epm = ep.ExpertParallelMoe(eng, CFG, capacity_rows=cap) if world > 1 else None
+    cap = 0 if (world < 2 or zipf) else -(-13 * Ml * CFG["NU"] // (10 * world) // 8) * 8
+    if world < 2:
+        epm = None
+    elif args.ep_impl == "torch":                      # the loop in Python over torch.distributed, stage by stage
+        epm = ep.ExpertParallelMoe(eng, CFG, capacity_rows=cap)
+    else:                                              # the loop inside the library: NCCL from C++, token slices pipelined
+        epm = ep.NcclExpertParallel(eng, CFG, capacity_rows=cap, slices=args.ep_slices)
 
     def one_pass():
         if epm is None:
@@ -436,6 +441,7 @@ def prefill_leg(args, eng, NL, PT, rank, local_rank, world, dist, barrier, zipf=
             "ms_per_pass": ms / passes, "passes": passes, "dtype": "f16 x f16 split operands (3 MMAs per k-step), f32 accumulate in TMEM",
             "parallelism": "single GPU" if world == 1 else f"expert-parallel: {PT // world} tokens and {CFG['NE'] // world} experts per GPU, all-to-all each way",
             "exchange": "none" if world == 1 else (f"padded: {cap} rows per destination, no host read per layer" if cap else "exact: split sizes read on the host once per layer"),
+            "driver": "none" if world == 1 else ("torch.distributed loop over the stage entries" if args.ep_impl == "torch" else f"sp_moe_ep_forward_dev (NCCL called from the library, {args.ep_slices if cap else 1} token slice(s) in flight)"),
             "expert_rows_last_layer": {"max_per_gpu": rows_max, "min_per_gpu": rows_min, "mean_per_gpu": float(PT * CFG["NU"]) / world,
                                        "max_over_mean": rows_max * world / float(PT * CFG["NU"]) if not cap else None},
             "parity": {"checked": what, "bit_identical": same, "finite": finite},
@@ -596,6 +602,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=4096, help="tokens of the prefill leg (whole job)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill leg")
     ap.add_argument("--no-ep-graph", action="store_true", help="run the expert-parallel prefill pass eagerly instead of from a CUDA graph")
+    ap.add_argument("--ep-impl", default="library", choices=["library", "torch"], help="who drives the expert-parallel layers: the library's own NCCL loop, or the Python loop over torch.distributed")
+    ap.add_argument("--ep-slices", type=int, default=1, help="token slices the library's expert-parallel loop keeps in flight (1..4)")
     ap.add_argument("--zipf", type=float, default=0.0, help="add a Zipf(s) per-expert bias to every router for the WHOLE run (0 = unbiased; the default N>1 line already carries a `zipf` object)")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="profiling aid: a shorter stack than the workload's 30 layers (not a bench result)")
     args = ap.parse_args()

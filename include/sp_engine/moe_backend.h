@@ -88,6 +88,15 @@ int  sp_moe_close(sp_moe *h);
  * are HOST memory in sp_moe_upload_layer and DEVICE memory in sp_moe_upload_layer_dev. */
 int  sp_moe_upload_layer(sp_moe *h, int layer, const sp_moe_layer_weights *w);
 int  sp_moe_upload_layer_dev(sp_moe *h, int layer, const sp_moe_layer_weights *w);
+/* Fills every layer of the handle from a `.sp-model` file (include/sp_engine/sp_model.h:97-134): the MoE share of
+ * build_weights (CF:2222-2372) + moe_cache_init (CF:6773-6879) in one call. The file is memory-mapped and each
+ * tensor goes straight from the mapping into the arena. names: NULL for the defaults, or 18 printf templates (one
+ * %d = the layer) in the order router_w, router_scale, ffn_norm, post_ffw1, pre_ffw2, post_ffw2, post_ffw,
+ * dexps_scale, then codes and block scales of gate|up, down, shared gate, shared up, shared down (defaults:
+ * "blk.%d.ffn_gate_inp.weight", ..., "blk.%d.ffn_down.weight.bscale"; a tensor "blk.%d.ffn_gate_inp.bias", when
+ * present, becomes the router bias). Checked: magic, layout rules, header CRC-32, each tensor's bounds,
+ * alignment, dtype, byte size and name hash; the per-tensor blake3 digest is not (no BLAKE3 in this library). */
+int  sp_moe_load_sp_model(sp_moe *h, const char *path, const char *const *names);
 /* Replaces only the router's per-expert logit bias of one layer (DEVICE pointer to NE floats, or NULL for
  * no bias); the other tensors stay as uploaded. The reference adds such a bias where the model file carries
  * one (`ffn_gate_inp.bias`, read with the router in build_weights, CF:2258-2268); load-imbalance experiments
@@ -151,6 +160,29 @@ int sp_moe_ep_experts_dev(sp_moe *h, int layer, int flavour, int n_rows, const f
                           void *stream);
 int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const float *pair_rows_dev,
                          const int32_t *pair_index_dev, float *y_dev, void *stream);
+
+/* The whole expert-parallel loop in one call: layers [layer_first, layer_first + n_layers) over n_ranks GPUs (one
+ * process each; this rank's tokens x_dev[M][E] in, y_dev[M][E] out, DEVICE pointers), the five stages above driven
+ * from inside the library with NCCL doing the count gather and the two exchanges of every layer (ncclAllGather,
+ * ncclSend / ncclRecv groups). nccl_comm: an ncclComm_t of the n_ranks processes, passed as void* - the caller's
+ * own, or one made with the helpers below. NCCL is looked up at run time (libnccl.so.2), not linked.
+ *   capacity_rows > 0 : padded exchange - room per destination rank for the whole call; no host read, the call
+ *                       only enqueues (kernels on `stream`, NCCL on an internal stream, events between them) and
+ *                       can be captured into a CUDA graph. slices (1..4): the tokens are handled as that many
+ *                       independent slices, so one slice's exchanges run under another's expert GEMMs. A block
+ *                       that does not fit is reported by sp_moe_status; rerun with capacity_rows = 0.
+ *   capacity_rows == 0: exact exchange - split sizes read on the host once per layer (the call synchronises).
+ * Needs max_expert_rows of the config >= n_ranks * capacity (padded) or the rows this rank can receive (exact).
+ * The first call allocates the exchange buffers (make it before any capture). Bit-identical to sp_moe_forward_dev. */
+int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, int rank, int layer_first, int n_layers, int flavour,
+                          int M, const float *x_dev, float *y_dev, int capacity_rows, int slices, void *stream);
+/* rows this rank's experts processed in the last layer of the last sp_moe_ep_forward_dev call */
+long long sp_moe_ep_last_rows(const sp_moe *h);
+/* Communicator helpers for callers without NCCL headers: 128 opaque bytes from one rank (ncclGetUniqueId), handed to
+ * every rank by whatever channel the job has, then one communicator per rank on its current CUDA device. */
+int sp_moe_ep_unique_id(void *id128);
+int sp_moe_ep_comm_create(const void *id128, int n_ranks, int rank, void **comm_out);
+int sp_moe_ep_comm_destroy(void *comm);
 
 /* The reference's standalone single-token operator, verbatim signature (CF:13821-13825).
  * All pointers are HOST memory; allocates, uploads the whole expert set, runs, frees.

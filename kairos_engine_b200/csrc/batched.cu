@@ -31,6 +31,7 @@ struct BView {                 /* carved scratch */
 };
 
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+constexpr int kSlices = SP_BATCHED_MAX_SLICES;     /* token slices of one layer that may be between route and finish at the same time */
 
 template <class F>
 size_t blayout(const SpDims &d, int Mx, int Rx, F place) {
@@ -43,9 +44,9 @@ size_t blayout(const SpDims &d, int Mx, int Rx, F place) {
     take(M * E); take(M * E); take(M * FFS); take(R * FFE);                                          /* q */
     take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * R * (FFE / 16));        /* s */
     take(4 * M * (E / 16)); take(4 * M * (E / 16)); take(4 * M * (FFS / 16)); take(4 * R * (FFE / 16));        /* c */
-    take(4 * M * NU); take(4 * NE); take(4 * NE * M);                                               /* sel_asc count list */
+    take(4 * M * NU); take(4 * NE * kSlices); take(4 * NE * M);                                     /* sel_asc count list */
     take(R * E); take(4 * R * (E / 16)); take(4 * R * (E / 16));                                    /* ep_q ep_s ep_c */
-    take(4 * M * NU); take(4 * (NE + 1));                                                           /* pairpos ep_off */
+    take(4 * M * NU); take(4 * (NE + 1) * kSlices);                                                 /* pairpos ep_off */
     return o;
 }
 BView bview(const SpDims &d, const SpBatchedScratch *s) {
@@ -59,6 +60,22 @@ BView bview(const SpDims &d, const SpBatchedScratch *s) {
     v.nx_c = (int *)p[19]; v.in_c = (int *)p[20]; v.hd_c = (int *)p[21]; v.h_c = (int *)p[22];
     v.sel_asc = (int *)p[23]; v.count = (int *)p[24]; v.list = (int *)p[25];
     v.ep_q = (signed char *)p[26]; v.ep_s = (float *)p[27]; v.ep_c = (int *)p[28]; v.pairpos = (int *)p[29]; v.ep_off = (int *)p[30];
+    return v;
+}
+/* The same scratch seen by token slice `slice` of a layer, whose first token is `t0`: everything the route stage
+ * leaves for the finish stage (per-token and per-pair rows, the per-expert counters) moves to the slice's own
+ * place, so several slices of one layer can be between route and finish at once (an expert-parallel run pipelines
+ * them). What only the experts stage uses (h, the received rows' quantised copies) is shared: that stage runs one
+ * slice at a time. */
+BView bview_slice(const SpDims &d, const SpBatchedScratch *s, int t0, int slice) {
+    BView v = bview(d, s);
+    const size_t E = d.E, NE = d.NE, NU = d.NU, FFS = d.FFS, t = (size_t)t0;
+    v.rin += t * E; v.nx_f += t * E; v.in_f += t * E; v.logits += t * NE; v.cw += t * NU; v.hd += t * FFS; v.dn += t * E; v.eo += t * NU * E;
+    v.nx_q += t * E; v.in_q += t * E; v.hd_q += t * FFS;
+    v.nx_s += t * (E / 16); v.in_s += t * (E / 16); v.hd_s += t * (FFS / 16);
+    v.nx_c += t * (E / 16); v.in_c += t * (E / 16); v.hd_c += t * (FFS / 16);
+    v.sel_asc += t * NU; v.pairpos += t * NU; v.list += t * NE;
+    v.count += (size_t)slice * NE; v.ep_off += (size_t)slice * (NE + 1);
     return v;
 }
 
@@ -611,10 +628,10 @@ cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float 
 
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
                                 float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, int n_ranks, int capacity,
-                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0, int slice) {
     *nlaunch = 0;
-    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
-    BView v = bview(d, s);
+    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices) return cudaErrorInvalidValue;
+    BView v = bview_slice(d, s, t0, slice);
     return flavour == SP_MOE_FLAVOUR_DECODE ? ep_route<true>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, n_ranks, capacity, v, s->tc, status, st, nlaunch)
                                             : ep_route<false>(d, L, M, x, sel_asc, cw, rows, counts, pair_index, sel, wts, defer_shared, n_ranks, capacity, v, s->tc, status, st, nlaunch);
 }
@@ -625,10 +642,10 @@ cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all
     k_b_recv_layout<<<1, 256, (size_t)(3 * nb + 1) * sizeof(int), st>>>(counts_all, d.NE, n_ranks, rank, capacity, offsets, row_index);
     return cudaGetLastError();
 }
-cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0, int slice) {
     *nlaunch = 0;
-    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
-    BView v = bview(d, s);
+    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices) return cudaErrorInvalidValue;
+    BView v = bview_slice(d, s, t0, slice);
     return flavour == SP_MOE_FLAVOUR_DECODE ? ep_shared<true>(d, L, M, v, s->tc, status, st, nlaunch) : ep_shared<false>(d, L, M, v, s->tc, status, st, nlaunch);
 }
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
@@ -640,10 +657,10 @@ cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flav
                                             : ep_experts<false>(d, L, R, rows_in, row_index, offsets, rows_out, v, s->tc, status, st, nlaunch);
 }
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,
-                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch) {
+                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch, int t0, int slice) {
     *nlaunch = 0;
-    if (!s->base || M > s->max_tokens) return cudaErrorInvalidValue;
-    BView v = bview(d, s);
+    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices) return cudaErrorInvalidValue;
+    BView v = bview_slice(d, s, t0, slice);
     k_b_finish<<<M, 256, (size_t)2 * d.E * 4, st>>>(d, L, x, v, pair_rows, pair_index, y); (*nlaunch)++;
     return cudaGetLastError();
 }

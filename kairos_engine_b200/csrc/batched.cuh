@@ -3,6 +3,8 @@
 #pragma once
 #include "common.cuh"
 
+#define SP_BATCHED_MAX_SLICES 4
+
 struct SpBatchedScratch {
     void *base;            /* one allocation carved into the buffers the kernels use */
     size_t bytes;
@@ -26,16 +28,19 @@ cudaError_t sp_batched_forward(const SpDims &d, const SpLayerDev *layers_host, i
  *             expert), pair_index[M*NU] (where pair t*NU+k sits in rows)
  *   experts : R rows; sorted position p (expert e owns positions [offsets[e], offsets[e+1])) is row
  *             row_index[p] of rows_in and of rows_out (NULL = the rows are already sorted); R <= max_rows
- *   finish  : output of token t's k-th expert (ascending id) = pair_rows[pair_index[t*NU+k]] (NULL = t*NU+k) */
+ *   finish  : output of token t's k-th expert (ascending id) = pair_rows[pair_index[t*NU+k]] (NULL = t*NU+k)
+ * t0 / slice: the tokens of one layer may be handled as up to SP_BATCHED_MAX_SLICES independent slices (slice i =
+ * M tokens starting at token t0 of the handle's max_tokens) that are between route and finish at the same time;
+ * route, shared and finish of a slice must name the same (t0, slice). The experts stage is per call. */
 cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavour, int M, const float *x, int32_t *sel_asc, float *cw,
                                 float *rows, int32_t *counts, int32_t *pair_index, int32_t *sel, float *wts, int defer_shared, int n_ranks, int capacity,
-                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+                                SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);
 /* receive side of the padded exchange (route called with a capacity): offsets[NE+1] and row_index[n_ranks*capacity] */
 cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all, int n_ranks, int rank, int capacity, int32_t *offsets, int32_t *row_index,
                                       cudaStream_t st, int *nlaunch);
 /* the shared expert of the tokens the last route call prepared, when that call deferred it */
-cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,
-                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch);
+                                 SpBatchedScratch *s, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);

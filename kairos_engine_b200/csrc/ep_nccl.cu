@@ -1,0 +1,371 @@
+/* ep_nccl.cu — the expert-parallel prefill loop behind the C ABI: one call runs a range of layers over
+ * n_ranks GPUs (one process each), NCCL doing the two exchanges of every layer.
+ *
+ * The reference is single-GPU: its batched branch walks every expert on the one device (CF:8925-8965 of
+ * src/backends/cuda/cuda_forward.cu). Here tokens are data-parallel (each rank owns the residual of its own
+ * tokens, the router, the shared expert and the norms) and the routed experts are partitioned contiguously,
+ * NE / n_ranks per rank. Per layer and token slice:
+ *
+ *   route (local) -> all-gather of the per-expert pair counts -> dispatch (all-to-all of the input rows)
+ *   -> experts (on the owner) -> combine (all-to-all of the output rows back) -> finish (local)
+ *
+ * Every NCCL call runs on an internal communication stream, every kernel on the caller's stream, and events
+ * order them, so with two or more token slices the dispatch of one slice and the combine of another run under
+ * the experts stage of a third, and the last combine of a layer runs under the first route of the next.
+ * The per-token combine still walks the experts in ascending id on the home rank: the result is bit-identical
+ * to sp_moe_forward_dev on one GPU.
+ *
+ * Two exchanges. Padded (capacity_rows > 0): every rank sends the same number of rows to every rank, the
+ * receive layout is built on the device, nothing waits for the host, and the whole call can be captured into a
+ * CUDA graph; a block that does not fit is reported by sp_moe_status. Exact (capacity_rows == 0): the split
+ * sizes are read on the host once per layer (one slice, no overlap).
+ *
+ * NCCL is not linked: its entry points are looked up at run time (the copy the process already holds - e.g. the
+ * one a framework loaded - or libnccl.so.2 from the loader's path), so a daemon that never runs
+ * expert-parallel needs no NCCL at all. No load uses cluster multicast; peers are reached through NCCL only.
+ */
+#include "handle.cuh"
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <dlfcn.h>
+#include <mutex>
+#include <new>
+
+namespace {
+
+/* the handful of NCCL declarations this file needs (nccl.h: opaque communicator, 128-byte unique id) */
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef int ncclResult_t;
+enum { ncclInt8 = 0, ncclInt32 = 2, ncclFloat32 = 7 };
+
+struct Nccl {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Send)(const void *, size_t, int, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Recv)(void *, size_t, int, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*GroupStart)();
+    ncclResult_t (*GroupEnd)();
+    const char *(*GetErrorString)(ncclResult_t);
+    bool ok = false;
+};
+Nccl g_nccl;
+std::once_flag g_nccl_once;
+
+const Nccl *nccl() {
+    std::call_once(g_nccl_once, [] {
+        void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);      /* an already-loaded copy with this name is reused */
+        if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) return;
+        auto sym = [&](const char *n) { return dlsym(lib, n); };
+        g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId))sym("ncclGetUniqueId");
+        g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))sym("ncclCommInitRank");
+        g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))sym("ncclCommDestroy");
+        g_nccl.AllGather = (decltype(g_nccl.AllGather))sym("ncclAllGather");
+        g_nccl.Send = (decltype(g_nccl.Send))sym("ncclSend");
+        g_nccl.Recv = (decltype(g_nccl.Recv))sym("ncclRecv");
+        g_nccl.GroupStart = (decltype(g_nccl.GroupStart))sym("ncclGroupStart");
+        g_nccl.GroupEnd = (decltype(g_nccl.GroupEnd))sym("ncclGroupEnd");
+        g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))sym("ncclGetErrorString");
+        g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllGather && g_nccl.Send && g_nccl.Recv &&
+                    g_nccl.GroupStart && g_nccl.GroupEnd && g_nccl.GetErrorString;
+    });
+    return g_nccl.ok ? &g_nccl : nullptr;
+}
+
+int fail(int code, const char *fmt, ...) {
+    char msg[512];
+    va_list ap; va_start(ap, fmt); vsnprintf(msg, sizeof msg, fmt, ap); va_end(ap);
+    sp_set_error(msg);
+    return code;
+}
+#define CK(call, where) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(e_ == cudaErrorMemoryAllocation ? SP_MOE_EBACKEND_OOM : SP_MOE_ECUDA, "sp_moe_ep_forward_dev: %s: %s", where, cudaGetErrorString(e_)); } while (0)
+int fail_nccl(const char *where, const char *what) {
+    char msg[512];
+    snprintf(msg, sizeof msg, "sp_moe_ep_forward_dev: %s: NCCL: %s", where, what ? what : "?");
+    sp_set_error(msg);
+    return SP_MOE_ECUDA;
+}
+#define NK(call, where) do { ncclResult_t r_ = (call); if (r_ != 0) return fail_nccl(where, N->GetErrorString(r_)); } while (0)
+
+constexpr int kMaxSlices = SP_BATCHED_MAX_SLICES;
+
+struct Slice {                      /* everything one token slice keeps between its stages */
+    int32_t *sel_asc, *counts, *pair_index, *counts_all, *offsets, *row_index;
+    float *cw, *send, *recv, *out, *back;
+    cudaEvent_t routed, gathered, dispatched, computed, combined;
+};
+struct EpState {
+    int device, n_ranks, max_tokens, rows_cap;      /* rows_cap: rows each of send / recv / out / back holds */
+    unsigned char *base; size_t bytes;
+    float *xa, *xb;                                 /* residual between layers */
+    Slice sl[kMaxSlices];
+    int32_t *counts_host;                           /* page-locked, exact exchange */
+    cudaStream_t comm;                              /* every NCCL call */
+    long long last_rows;
+};
+
+void ep_free(void *p) {
+    EpState *s = (EpState *)p;
+    if (!s) return;
+    cudaSetDevice(s->device);
+    if (s->comm) { cudaStreamSynchronize(s->comm); cudaStreamDestroy(s->comm); }
+    for (auto &x : s->sl) for (cudaEvent_t e : {x.routed, x.gathered, x.dispatched, x.computed, x.combined}) if (e) cudaEventDestroy(e);
+    if (s->base) cudaFree(s->base);
+    if (s->counts_host) cudaFreeHost(s->counts_host);
+    delete s;
+}
+
+/* rows the exchange buffers hold: the handle's max_expert_rows covers both the worst exact exchange and
+ * n_ranks * capacity of a padded one (sp_moe_ep_recv_layout_dev checks the same bound) */
+int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
+    EpState *s = (EpState *)h->ep_state;
+    if (s && s->n_ranks == n_ranks) { *out = s; return SP_MOE_OK; }
+    if (s) { ep_free(s); h->ep_state = nullptr; }
+    s = new (std::nothrow) EpState();
+    if (!s) return fail(SP_MOE_ENOMEM, "sp_moe_ep_forward_dev: host OOM");
+    memset(s, 0, sizeof *s);
+    s->device = h->device; s->n_ranks = n_ranks; s->max_tokens = h->cfg.max_tokens; s->rows_cap = h->bs.max_rows;
+    const size_t E = h->cfg.E, NE = h->cfg.NE, NU = h->cfg.NU, MT = (size_t)s->max_tokens, R = (size_t)s->rows_cap;
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    /* the slices share the token range and the row buffers: slice k of n uses its own part of each */
+    size_t o = 0;
+    auto take = [&](size_t bytes) { const size_t at = o; o = up(o + bytes); return at; };
+    const size_t o_xa = take(4 * MT * E), o_xb = take(4 * MT * E), o_sel = take(4 * MT * NU), o_cw = take(4 * MT * NU), o_pi = take(4 * MT * NU);
+    const size_t o_cnt = take(4 * NE * kMaxSlices), o_call = take(4 * NE * (size_t)n_ranks * kMaxSlices), o_off = take(4 * (NE + 1) * kMaxSlices), o_ri = take(4 * R);
+    const size_t o_send = take(4 * R * E), o_recv = take(4 * R * E), o_out = take(4 * R * E), o_back = take(4 * R * E);
+    s->bytes = o;
+    cudaError_t e = cudaMalloc(&s->base, s->bytes);
+    if (e != cudaSuccess) { delete s; return fail(SP_MOE_EBACKEND_OOM, "sp_moe_ep_forward_dev: exchange buffers (%lld MB): cuda error %lld", (long long)(o >> 20), (long long)e); }
+    unsigned char *b = s->base;
+    s->xa = (float *)(b + o_xa); s->xb = (float *)(b + o_xb);
+    for (int k = 0; k < kMaxSlices; k++) {
+        Slice &x = s->sl[k];
+        x.sel_asc = (int32_t *)(b + o_sel); x.cw = (float *)(b + o_cw); x.pair_index = (int32_t *)(b + o_pi);          /* + token offset at use */
+        x.counts = (int32_t *)(b + o_cnt) + (size_t)k * NE; x.counts_all = (int32_t *)(b + o_call) + (size_t)k * NE * n_ranks;
+        x.offsets = (int32_t *)(b + o_off) + (size_t)k * (NE + 1); x.row_index = (int32_t *)(b + o_ri);                  /* + row offset at use */
+        x.send = (float *)(b + o_send); x.recv = (float *)(b + o_recv); x.out = (float *)(b + o_out); x.back = (float *)(b + o_back);
+        for (cudaEvent_t *ev : {&x.routed, &x.gathered, &x.dispatched, &x.computed, &x.combined})
+            if (cudaEventCreateWithFlags(ev, cudaEventDisableTiming) != cudaSuccess) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
+    }
+    if (cudaMallocHost((void **)&s->counts_host, 4 * NE * (size_t)n_ranks) != cudaSuccess || cudaStreamCreateWithFlags(&s->comm, cudaStreamNonBlocking) != cudaSuccess) {
+        ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: stream / pinned buffer creation failed");
+    }
+    h->ep_state = s; h->ep_state_free = ep_free;
+    h->scratch_bytes += s->bytes;
+    *out = s;
+    return SP_MOE_OK;
+}
+
+}  // namespace
+
+/* ---------------------------------------------------------------- communicator helpers */
+extern "C" int sp_moe_ep_unique_id(void *id128) {
+    const Nccl *N = nccl();
+    if (!N) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_ep_unique_id: libnccl.so.2 is not available to this process");
+    if (!id128) return fail(SP_MOE_EBADARG, "sp_moe_ep_unique_id: NULL argument");
+    ncclUniqueId id;
+    const ncclResult_t r = N->GetUniqueId(&id);
+    if (r != 0) return fail(SP_MOE_ECUDA, "sp_moe_ep_unique_id: NCCL: %s", N->GetErrorString(r));
+    memcpy(id128, &id, sizeof id);
+    return SP_MOE_OK;
+}
+extern "C" int sp_moe_ep_comm_create(const void *id128, int n_ranks, int rank, void **comm_out) {
+    const Nccl *N = nccl();
+    if (!N) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_ep_comm_create: libnccl.so.2 is not available to this process");
+    if (!id128 || !comm_out || n_ranks <= 0 || rank < 0 || rank >= n_ranks) return fail(SP_MOE_EBADARG, "sp_moe_ep_comm_create: bad argument");
+    ncclUniqueId id; memcpy(&id, id128, sizeof id);
+    ncclComm_t c = nullptr;
+    const ncclResult_t r = N->CommInitRank(&c, n_ranks, id, rank);      /* on the CUDA device current in this thread */
+    if (r != 0) return fail(SP_MOE_ECUDA, "sp_moe_ep_comm_create: NCCL: %s", N->GetErrorString(r));
+    *comm_out = c;
+    return SP_MOE_OK;
+}
+extern "C" int sp_moe_ep_comm_destroy(void *comm) {
+    const Nccl *N = nccl();
+    if (!comm) return SP_MOE_OK;
+    if (!N) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_ep_comm_destroy: libnccl.so.2 is not available to this process");
+    const ncclResult_t r = N->CommDestroy((ncclComm_t)comm);
+    return r == 0 ? SP_MOE_OK : fail(SP_MOE_ECUDA, "sp_moe_ep_comm_destroy: NCCL: %s", N->GetErrorString(r));
+}
+extern "C" long long sp_moe_ep_last_rows(const sp_moe *h) { return (h && h->ep_state) ? ((const EpState *)h->ep_state)->last_rows : 0; }
+
+/* ---------------------------------------------------------------- the layer loop */
+extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, int rank, int lf, int nl, int flavour, int M,
+                                     const float *x_dev, float *y_dev, int capacity_rows, int slices, void *stream) {
+    const Nccl *N = nccl();
+    if (!N) return fail(SP_MOE_EUNSUPPORTED, "sp_moe_ep_forward_dev: libnccl.so.2 is not available to this process");
+    if (!h || !nccl_comm || !x_dev || !y_dev) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: NULL argument");
+    const sp_moe_config &c = h->cfg;
+    if (n_ranks <= 0 || c.NE % n_ranks || rank < 0 || rank >= n_ranks) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: need 0 <= rank < n_ranks and n_ranks dividing NE");
+    if (lf < 0 || nl <= 0 || lf + nl > c.n_layers) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: layers out of range");
+    if (M <= 0 || M > c.max_tokens) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: M=%d outside (0, max_tokens=%d]", M, c.max_tokens);
+    if (flavour != SP_MOE_FLAVOUR_DECODE && flavour != SP_MOE_FLAVOUR_PREFILL) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: unknown flavour");
+    for (int L = lf; L < lf + nl; L++) if (!h->uploaded[L]) return fail(SP_MOE_EBADSTATE, "sp_moe_ep_forward_dev: layer %d has no weights uploaded", L);
+    if (capacity_rows < 0) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: capacity_rows must not be negative");
+    const bool padded = capacity_rows > 0;
+    int ns = padded ? (slices < 1 ? 1 : (slices > kMaxSlices ? kMaxSlices : slices)) : 1;
+    if (ns > M) ns = M;
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    EpState *s = nullptr;
+    { const int rc = ep_ensure(h, n_ranks, &s); if (rc) return rc; }
+    const int E = c.E, NE = c.NE, NU = c.NU, epr = NE / n_ranks;
+    /* per-slice capacity: the per-destination room of the whole call split over the slices, in multiples of 8 rows */
+    const int cap = padded ? ((capacity_rows + ns - 1) / ns + 7) / 8 * 8 : 0;
+    if (padded && (long long)n_ranks * cap * ns > s->rows_cap)
+        return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: %d slices x n_ranks x %d rows = %lld rows exceed max_expert_rows = %d", ns, cap, (long long)n_ranks * cap * ns, s->rows_cap);
+    if (!padded && (long long)M * NU > s->rows_cap) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: M * NU exceeds max_expert_rows");
+    cudaStream_t st = (cudaStream_t)stream, cs = s->comm;
+    ncclComm_t comm = (ncclComm_t)nccl_comm;
+    h->last_stream = st;
+    int nlaunch = 0, nlk = 0;
+    const SpDims &d = h->d;
+    /* token range and row range of every slice */
+    int t0[kMaxSlices], tm[kMaxSlices]; size_t r0[kMaxSlices];
+    for (int k = 0; k < ns; k++) { t0[k] = (int)((long long)M * k / ns); tm[k] = (int)((long long)M * (k + 1) / ns) - t0[k]; r0[k] = padded ? (size_t)k * n_ranks * cap : 0; }
+
+    const float *cur = x_dev;
+    for (int li = 0; li < nl; li++) {
+        const int L = lf + li;
+        const SpLayerDev &W = h->layers_host[L];
+        float *dst = (li == nl - 1) ? y_dev : ((li & 1) ? s->xb : s->xa);
+        if (padded) {
+            /* ---- route every slice; its count gather and its dispatch follow on the communication stream */
+            for (int k = 0; k < ns; k++) {
+                Slice &x = s->sl[k];
+                cudaError_t e = sp_batched_ep_route(d, W, flavour, tm[k], cur + (size_t)t0[k] * E, x.sel_asc + (size_t)t0[k] * NU, x.cw + (size_t)t0[k] * NU,
+                                                    x.send + r0[k] * E, x.counts, x.pair_index + (size_t)t0[k] * NU, nullptr, nullptr, 1, n_ranks, cap,
+                                                    &h->bs, h->status, st, &nlk, t0[k], k);
+                nlaunch += nlk;
+                CK(e, "route");
+                CK(cudaEventRecord(x.routed, st), "event record");
+                CK(cudaStreamWaitEvent(cs, x.routed, 0), "event wait");
+                NK(N->AllGather(x.counts, x.counts_all, (size_t)NE, ncclInt32, comm, cs), "all-gather of the counts");
+                CK(cudaEventRecord(x.gathered, cs), "event record");
+                NK(N->GroupStart(), "group start");
+                for (int r = 0; r < n_ranks; r++) {
+                    NK(N->Send(x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch send");
+                    NK(N->Recv(x.recv + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                }
+                NK(N->GroupEnd(), "group end");
+                CK(cudaEventRecord(x.dispatched, cs), "event record");
+            }
+            /* ---- per slice: the shared expert and the receive layout (under the dispatch), the experts, the combine */
+            for (int k = 0; k < ns; k++) {
+                Slice &x = s->sl[k];
+                cudaError_t e = sp_batched_ep_shared(d, W, flavour, tm[k], &h->bs, h->status, st, &nlk, t0[k], k);
+                nlaunch += nlk;
+                CK(e, "shared expert");
+                CK(cudaStreamWaitEvent(st, x.gathered, 0), "event wait");
+                e = sp_batched_ep_recv_layout(d, x.counts_all, n_ranks, rank, cap, x.offsets, x.row_index + r0[k], st, &nlk);
+                nlaunch += nlk;
+                CK(e, "receive layout");
+                CK(cudaStreamWaitEvent(st, x.dispatched, 0), "event wait");
+                e = sp_batched_ep_experts(d, W, flavour, n_ranks * cap, x.recv + r0[k] * E, x.row_index + r0[k], x.offsets, x.out + r0[k] * E, &h->bs, h->status, st, &nlk);
+                nlaunch += nlk;
+                CK(e, "experts");
+                CK(cudaEventRecord(x.computed, st), "event record");
+                CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
+                NK(N->GroupStart(), "group start");
+                for (int r = 0; r < n_ranks; r++) {
+                    NK(N->Send(x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine send");
+                    NK(N->Recv(x.back + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine recv");
+                }
+                NK(N->GroupEnd(), "group end");
+                CK(cudaEventRecord(x.combined, cs), "event record");
+            }
+            /* ---- finish every slice as its rows come back */
+            for (int k = 0; k < ns; k++) {
+                Slice &x = s->sl[k];
+                CK(cudaStreamWaitEvent(st, x.combined, 0), "event wait");
+                cudaError_t e = sp_batched_ep_finish(d, W, tm[k], cur + (size_t)t0[k] * E, x.back + r0[k] * E, x.pair_index + (size_t)t0[k] * NU, dst + (size_t)t0[k] * E,
+                                                     &h->bs, st, &nlk, t0[k], k);
+                nlaunch += nlk;
+                CK(e, "finish");
+            }
+            s->last_rows = (long long)n_ranks * cap * ns;
+        } else {
+            /* ---- exact exchange: one slice, the split sizes read on the host */
+            Slice &x = s->sl[0];
+            cudaError_t e = sp_batched_ep_route(d, W, flavour, M, cur, x.sel_asc, x.cw, x.send, x.counts, x.pair_index, nullptr, nullptr, 1, 0, 0, &h->bs, h->status, st, &nlk, 0, 0);
+            nlaunch += nlk;
+            CK(e, "route");
+            CK(cudaEventRecord(x.routed, st), "event record");
+            CK(cudaStreamWaitEvent(cs, x.routed, 0), "event wait");
+            NK(N->AllGather(x.counts, x.counts_all, (size_t)NE, ncclInt32, comm, cs), "all-gather of the counts");
+            CK(cudaMemcpyAsync(s->counts_host, x.counts_all, 4 * (size_t)NE * n_ranks, cudaMemcpyDeviceToHost, cs), "counts D2H");
+            CK(cudaStreamSynchronize(cs), "stream synchronize");               /* the one host read of the layer */
+            long long send_n[64 * 16], recv_n[64 * 16];
+            if (n_ranks > 1024) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: more than 1024 ranks");
+            long long R = 0, soff = 0;
+            for (int r = 0; r < n_ranks; r++) {
+                long long a = 0, b2 = 0;
+                for (int q = 0; q < epr; q++) { a += s->counts_host[(size_t)rank * NE + r * epr + q]; b2 += s->counts_host[(size_t)r * NE + rank * epr + q]; }
+                send_n[r] = a; recv_n[r] = b2; R += b2;
+            }
+            if (R > s->rows_cap) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: this rank would receive %lld rows, max_expert_rows is %d", R, s->rows_cap);
+            NK(N->GroupStart(), "group start");
+            { long long ro = 0; soff = 0;
+              for (int r = 0; r < n_ranks; r++) {
+                  if (send_n[r]) NK(N->Send(x.send + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "dispatch send");
+                  if (recv_n[r]) NK(N->Recv(x.recv + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                  soff += send_n[r]; ro += recv_n[r];
+              } }
+            NK(N->GroupEnd(), "group end");
+            CK(cudaEventRecord(x.dispatched, cs), "event record");
+            e = sp_batched_ep_shared(d, W, flavour, M, &h->bs, h->status, st, &nlk, 0, 0);
+            nlaunch += nlk;
+            CK(e, "shared expert");
+            /* the rows arrive source-major, each source's block sorted by expert: the layout kernel with a capacity
+             * equal to each source's real block would need per-source capacities, so build it here on the host */
+            {
+                static thread_local std::vector<int32_t> off, idx;
+                off.assign((size_t)NE + 1, 0); idx.resize((size_t)R);
+                std::vector<long long> arrival((size_t)n_ranks + 1, 0);
+                for (int r = 0; r < n_ranks; r++) arrival[r + 1] = arrival[r] + recv_n[r];
+                long long p = 0;
+                std::vector<long long> within((size_t)n_ranks, 0);
+                for (int q = 0; q < epr; q++) {
+                    off[(size_t)rank * epr + q] = (int32_t)p;
+                    for (int r = 0; r < n_ranks; r++) {
+                        const int cnt = s->counts_host[(size_t)r * NE + rank * epr + q];
+                        for (int i = 0; i < cnt; i++) idx[(size_t)p++] = (int32_t)(arrival[r] + within[r] + i);
+                        within[r] += cnt;
+                    }
+                }
+                for (int eidx = rank * epr + epr; eidx <= NE; eidx++) off[(size_t)eidx] = (int32_t)R;
+                CK(cudaMemcpyAsync(x.offsets, off.data(), 4 * ((size_t)NE + 1), cudaMemcpyHostToDevice, st), "offsets H2D");
+                if (R) CK(cudaMemcpyAsync(x.row_index, idx.data(), 4 * (size_t)R, cudaMemcpyHostToDevice, st), "row index H2D");
+                CK(cudaStreamSynchronize(st), "stream synchronize");             /* the staging vectors are reused by the next layer */
+            }
+            CK(cudaStreamWaitEvent(st, x.dispatched, 0), "event wait");
+            if (R) {
+                e = sp_batched_ep_experts(d, W, flavour, (int)R, x.recv, x.row_index, x.offsets, x.out, &h->bs, h->status, st, &nlk);
+                nlaunch += nlk;
+                CK(e, "experts");
+            }
+            CK(cudaEventRecord(x.computed, st), "event record");
+            CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
+            NK(N->GroupStart(), "group start");
+            { long long ro = 0; soff = 0;
+              for (int r = 0; r < n_ranks; r++) {
+                  if (recv_n[r]) NK(N->Send(x.out + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "combine send");
+                  if (send_n[r]) NK(N->Recv(x.back + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "combine recv");
+                  soff += send_n[r]; ro += recv_n[r];
+              } }
+            NK(N->GroupEnd(), "group end");
+            CK(cudaEventRecord(x.combined, cs), "event record");
+            CK(cudaStreamWaitEvent(st, x.combined, 0), "event wait");
+            e = sp_batched_ep_finish(d, W, M, cur, x.back, x.pair_index, dst, &h->bs, st, &nlk, 0, 0);
+            nlaunch += nlk;
+            CK(e, "finish");
+            s->last_rows = R;
+        }
+        cur = dst;
+    }
+    h->launches += (uint64_t)nlaunch;
+    return SP_MOE_OK;
+}

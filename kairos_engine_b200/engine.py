@@ -76,6 +76,16 @@ class MoeEngine:
         fn = _lib.lib().sp_moe_upload_layer_dev if on_device else _lib.lib().sp_moe_upload_layer
         check(fn(self._h, layer, C.byref(w)))
 
+    def load_sp_model(self, path, names=None):
+        """Fills every layer from a `.sp-model` file through the library's own loader (sp_moe_load_sp_model).
+        names: None, or 18 printf-style templates (see the header)."""
+        arr = None
+        if names is not None:
+            if len(names) != 18:
+                raise ValueError("names must hold 18 templates")
+            arr = (C.c_char_p * 18)(*[n.encode() for n in names])
+        check(_lib.lib().sp_moe_load_sp_model(self._h, str(path).encode(), arr))
+
     def set_router_bias(self, layer, bias):
         """Replaces the router's per-expert logit bias of one layer (torch CUDA f32 [NE], or None for no bias)."""
         check(_lib.lib().sp_moe_set_router_bias_dev(self._h, layer, _ptr(bias)))

@@ -125,3 +125,46 @@ class ExpertParallelMoe:
         for L in range(layer_first, layer_first + n_layers):
             x = self.layer(L, x, flavour)
         return x
+
+
+class NcclExpertParallel:
+    """The same loop run inside the library (sp_moe_ep_forward_dev): NCCL called from C++, exchanges on an internal
+    stream under the expert GEMMs of other token slices. torch.distributed is used once, to hand rank 0's NCCL id
+    to the other ranks; the communicator is the library's own."""
+
+    def __init__(self, engine, cfg, group=None, capacity_rows=0, slices=2):
+        import ctypes as C
+        from . import _lib
+        self.engine, self.cfg = engine, cfg
+        self.capacity, self.slices = int(capacity_rows), int(slices)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if cfg["NE"] % self.world:
+            raise ValueError(f"NE={cfg['NE']} is not divisible by the world size {self.world}")
+        L = _lib.lib()
+        ident = (C.c_ubyte * 128)()
+        if self.rank == 0:
+            _lib.check(L.sp_moe_ep_unique_id(ident))
+        box = [bytes(ident)]
+        dist.broadcast_object_list(box, src=0, group=group)
+        ident = (C.c_ubyte * 128).from_buffer_copy(box[0])
+        self._comm = C.c_void_p()
+        _lib.check(L.sp_moe_ep_comm_create(ident, self.world, self.rank, C.byref(self._comm)))
+
+    @property
+    def last_rows(self):
+        from . import _lib
+        return int(_lib.lib().sp_moe_ep_last_rows(self.engine._h))
+
+    def forward(self, x, layer_first=0, n_layers=1, flavour=1, out=None):
+        from . import _lib
+        y = torch.empty_like(x) if out is None else out
+        st = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.lib().sp_moe_ep_forward_dev(self.engine._h, self._comm, self.world, self.rank, layer_first, n_layers, flavour, x.shape[0],
+                                                   x.data_ptr(), y.data_ptr(), self.capacity, self.slices, st))
+        return y
+
+    def close(self):
+        from . import _lib
+        if getattr(self, "_comm", None) is not None and self._comm.value:
+            _lib.lib().sp_moe_ep_comm_destroy(self._comm)
+            self._comm = None

@@ -165,6 +165,12 @@ int main(void) {
         cudaFree(sel_asc); cudaFree(counts); cudaFree(pair_index); cudaFree(cw); cudaFree(rows); cudaFree(rows_out); cudaFree(y_st); cudaFree(off_dev); cudaFree(roff); cudaFree(ridx);
     }
 
+    /* ---- the file loader and the bias setter: refusals (a real file is the Python tests' job) */
+    CHECK(sp_moe_load_sp_model(h, "/nonexistent/model.sp-model", NULL) == SP_MOE_EBADARG && strstr(sp_last_error(), "cannot open") != NULL, "load_sp_model must refuse a missing file");
+    CHECK(sp_moe_load_sp_model(h, NULL, NULL) == SP_MOE_EBADARG, "load_sp_model must refuse NULL");
+    CHECK(sp_moe_set_router_bias_dev(h, 99, NULL) == SP_MOE_EBADARG, "set_router_bias must refuse a layer out of range");
+    CHECK(sp_moe_set_router_bias_dev(h, 1, NULL) == SP_MOE_OK, "sp_moe_set_router_bias_dev");
+
     /* ---- timing entry (not switched on here) and the failure-path probe */
     sp_moe_timing tm;
     CHECK(sp_moe_decode_timing(h, &tm) == (getenv("SP_MOE_TIMING") ? SP_MOE_OK : SP_MOE_EBADSTATE), "sp_moe_decode_timing without/with SP_MOE_TIMING");

@@ -178,7 +178,8 @@ def _free_port():
     return p
 
 
-def _nccl_rank(rank, world, port, flavour, q, capacity=0):
+def _nccl_rank(rank, world, port, cases, q):
+    """cases: list of (impl, flavour, capacity, slices). One process pair, one NCCL start-up, every case."""
     import torch
     import torch.distributed as dist
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -188,23 +189,36 @@ def _nccl_rank(rank, world, port, flavour, q, capacity=0):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         cfg, n_layers, M = orc.SMALL, 2, 24 + 8 * rank
-        eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, max_expert_rows=max(256, 2 * capacity), **cfg)
+        eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, max_expert_rows=512, **cfg)
         for L in range(n_layers):
             eng.upload_layer(L, synth.make_layer(cfg, 77 + 1000 * L, rand_norms=True, device=f"cuda:{rank}"), on_device=True)
         x = torch.from_numpy(np.random.default_rng(rank).standard_normal((M, cfg["E"])).astype(np.float32)).cuda()
-        want = torch.empty_like(x)
-        eng.forward_dev(x, want, 0, n_layers, flavour)
-        got = ep.ExpertParallelMoe(eng, cfg, capacity_rows=capacity).forward(x, 0, n_layers, flavour)
-        eng.status()
-        torch.cuda.synchronize()
-        q.put((rank, bool(torch.equal(got.view(torch.int32), want.view(torch.int32)))))
+        results = []
+        for impl, flavour, capacity, slices in cases:
+            want = torch.empty_like(x)
+            eng.forward_dev(x, want, 0, n_layers, flavour)
+            if impl == "library":                  # the loop inside the library: NCCL called from C++, token slices pipelined
+                drv = ep.NcclExpertParallel(eng, cfg, capacity_rows=capacity, slices=slices)
+                got = drv.forward(x, 0, n_layers, flavour)
+                again = drv.forward(x, 0, n_layers, flavour)      # buffers and events are reused across calls
+                eng.status()
+                torch.cuda.synchronize()
+                ok = bool(torch.equal(got.view(torch.int32), want.view(torch.int32))) and bool(torch.equal(again.view(torch.int32), want.view(torch.int32)))
+                ok = ok and drv.last_rows > 0
+                drv.close()
+            else:
+                got = ep.ExpertParallelMoe(eng, cfg, capacity_rows=capacity).forward(x, 0, n_layers, flavour)
+                eng.status()
+                torch.cuda.synchronize()
+                ok = bool(torch.equal(got.view(torch.int32), want.view(torch.int32)))
+            results.append(ok)
+        q.put((rank, results))
         eng.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("flavour,capacity", [(A, 0), (B, 0), (A, 160), (B, 160)])
-def test_two_gpus_nccl_equal_single_gpu(flavour, capacity):
+def _run_pair(cases):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -212,9 +226,23 @@ def test_two_gpus_nccl_equal_single_gpu(flavour, capacity):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, flavour, q, capacity)) for r in range(2)]
+    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, cases, q)) for r in range(2)]
     for p in ps: p.start()
-    got = [q.get(timeout=300) for _ in ps]
+    got = [q.get(timeout=600) for _ in ps]
     for p in ps:
         p.join(120); assert p.exitcode == 0
-    assert all(ok for _, ok in got), got
+    for rank, results in got:
+        bad = [c for c, ok in zip(cases, results) if not ok]
+        assert not bad, f"rank {rank}: not bit-identical to the single-GPU pass: {bad}"
+
+
+def test_two_gpus_nccl_equal_single_gpu():
+    """ExpertParallelMoe over torch.distributed (NCCL) == the single-GPU pass, bit for bit: both arithmetic
+    flavours, exact and padded exchange."""
+    _run_pair([("torch", A, 0, 1), ("torch", B, 0, 1), ("torch", A, 160, 1), ("torch", B, 160, 1)])
+
+
+def test_two_gpus_library_loop_equals_single_gpu():
+    """sp_moe_ep_forward_dev (the whole loop behind the C ABI, its own NCCL communicator) == the single-GPU pass,
+    bit for bit: exact and padded exchange, one to four token slices in flight."""
+    _run_pair([("library", B, 0, 1), ("library", A, 0, 1), ("library", B, 160, 1), ("library", B, 160, 2), ("library", A, 160, 3), ("library", B, 200, 4)])
