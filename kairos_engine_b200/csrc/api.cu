@@ -147,6 +147,9 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         h->decode_impl = ((ev && ev[0] == 'd') || !sp_staged_fits(h->d, h->sms, (size_t)optin)) ? 1 : 0;
         const char *fv = getenv("SP_MOE_STAGED_FLAGS");
         h->staged_flags = fv ? (unsigned)strtoul(fv, nullptr, 0) : (unsigned)SP_STAGED_DEFAULT;
+        const char *sq = getenv("SP_MOE_SEQ_TOKENS");              /* tuning switch: 1 sends every batch of 2+ tokens to the batched kernels */
+        h->seq_tokens = sq ? atoi(sq) : 8;
+        if (h->seq_tokens < 1) h->seq_tokens = 1;
         /* the kernels' shared-memory limits are a per-device setting: set them for this handle's device */
         OPEN_CK(sp_graph_prepare(), "decode kernel attributes");
         if (h->decode_impl == 0) OPEN_CK(sp_staged_prepare(h->d, h->sms), "decode kernel attributes");
@@ -256,7 +259,10 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
     CK(cudaSetDevice(h->device), "cudaSetDevice");
     cudaStream_t st = (cudaStream_t)stream;
     h->last_stream = st;
-    if (M == 1 && flavour == SP_MOE_FLAVOUR_DECODE) {
+    if (M <= h->seq_tokens && flavour == SP_MOE_FLAVOUR_DECODE) {
+        /* A handful of tokens goes through the single-token graph one token after the other: below
+         * seq_tokens that is faster than the batched kernels, and each row is the single-token result
+         * by construction. */
         const bool routing = sel_dev || wts_dev;
         sp_moe::DecodeGraph *dg = nullptr;
         for (auto &g : h->graphs) if (g.lf == lf && g.nl == nl && g.routing == routing) dg = &g;
@@ -278,13 +284,16 @@ extern "C" int sp_moe_forward_dev(sp_moe *h, int lf, int nl, int flavour, int M,
             h->graphs.push_back({lf, nl, routing, exec, nlaunch});
             dg = &h->graphs.back();
         }
-        const size_t nb = (size_t)h->cfg.E * 4, ns = (size_t)nl * h->cfg.NU * 4;
-        CK(cudaMemcpyAsync(h->g_x, x_dev, nb, cudaMemcpyDeviceToDevice, st), "x staging");
-        CK(cudaGraphLaunch(dg->exec, st), "decode graph launch");
-        CK(cudaMemcpyAsync(y_dev, h->g_y, nb, cudaMemcpyDeviceToDevice, st), "y staging");
-        if (sel_dev) CK(cudaMemcpyAsync(sel_dev, h->g_sel, ns, cudaMemcpyDeviceToDevice, st), "sel staging");
-        if (wts_dev) CK(cudaMemcpyAsync(wts_dev, h->g_wts, ns, cudaMemcpyDeviceToDevice, st), "wts staging");
-        h->launches += (uint64_t)dg->launches;
+        const size_t E = (size_t)h->cfg.E, NU = (size_t)h->cfg.NU, nb = E * 4;
+        for (int t = 0; t < M; t++) {
+            CK(cudaMemcpyAsync(h->g_x, x_dev + t * E, nb, cudaMemcpyDeviceToDevice, st), "x staging");
+            CK(cudaGraphLaunch(dg->exec, st), "decode graph launch");
+            CK(cudaMemcpyAsync(y_dev + t * E, h->g_y, nb, cudaMemcpyDeviceToDevice, st), "y staging");
+            /* routing tables are [layer][token][NU]: one NU-wide strip per layer for this token */
+            if (sel_dev) CK(cudaMemcpy2DAsync(sel_dev + t * NU, (size_t)M * NU * 4, h->g_sel, NU * 4, NU * 4, (size_t)nl, cudaMemcpyDeviceToDevice, st), "sel staging");
+            if (wts_dev) CK(cudaMemcpy2DAsync(wts_dev + t * NU, (size_t)M * NU * 4, h->g_wts, NU * 4, NU * 4, (size_t)nl, cudaMemcpyDeviceToDevice, st), "wts staging");
+            h->launches += (uint64_t)dg->launches;
+        }
         return SP_MOE_OK;
     }
     if (M <= 64) {

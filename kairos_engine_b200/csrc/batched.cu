@@ -121,21 +121,74 @@ __device__ __forceinline__ void quant_row(int n, signed char *q, float *sx, int 
 }
 
 /* ---------------------------------------------------------------- K1: per-token norms of x (CF:8347, 8402-8404, 8425) */
+/* block sum of 256 per-thread doubles in sumsq256's order */
+__device__ double block_sum256(double s, double *sh) {
+    const int t = threadIdx.x;
+    sh[t] = s;
+    __syncthreads();
+    for (int o = 128; o >= 32; o >>= 1) { if (t < o) sh[t] += sh[t + o]; __syncthreads(); }
+    if (t < 32) {
+        double a = sh[t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_down_sync(0xffffffffu, a, o);
+        if (t == 0) sh[0] = a;
+    }
+    __syncthreads();
+    const double r = sh[0];
+    __syncthreads();
+    return r;
+}
+/* One block per token. Everything a thread needs (its 256-strided elements of x and of the three norm
+ * vectors) is fetched before the first dependent step, so a block pays the memory latency once and not
+ * once per 256 elements; rows wider than 256 * kPrepK take the plain loops. */
+constexpr int kPrepK = 12;
 template <bool FA>
 __global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const float *x, BView v, float *rows_f) {
     __shared__ double sh[256];
-    const int t = blockIdx.x, E = d.E;
+    const int t = blockIdx.x, E = d.E, tid = threadIdx.x;
     const float *xt = x + (size_t)t * E;
-    if (t == 0) for (int i = threadIdx.x; i < d.NE; i += 256) v.count[i] = 0;
+    if (t == 0) for (int i = tid; i < d.NE; i += 256) v.count[i] = 0;
+    if (E <= 256 * kPrepK) {
+        float xv[kPrepK], n1[kPrepK], n2[kPrepK], rs[kPrepK];
+#pragma unroll
+        for (int k = 0; k < kPrepK; k++) {
+            const int i = tid + 256 * k; const bool ok = i < E;
+            xv[k] = ok ? xt[i] : 0.0f; n1[k] = ok ? __ldg(L.ffn_norm + i) : 0.0f;
+            n2[k] = ok ? __ldg(L.pre_ffw2 + i) : 0.0f; rs[k] = ok ? __ldg(L.router_scale + i) : 0.0f;
+        }
+        double ss = 0.0;
+#pragma unroll
+        for (int k = 0; k < kPrepK; k++) if (256 * k < E) { const double a = xv[k]; if (tid + 256 * k < E) ss += a * a; }
+        const float scale = rms_scale_from(block_sum256(ss, sh), E, d.eps);
+        const size_t b16 = (size_t)t * (E / 16), row = (size_t)t * E;
+#pragma unroll
+        for (int k = 0; k < kPrepK; k++) {
+            if (256 * k < E) {                                  /* block-uniform: every lane of a warp reaches the shuffles */
+                const int i = tid + 256 * k; const bool ok = i < E;
+                const float xs = __fmul_rn(xv[k], scale);
+                const float nv = __fmul_rn(xs, n1[k]), iv = __fmul_rn(xs, n2[k]);
+                if (FA) {
+                    const int b = i >> 4;
+                    quant_elem16(nv, ok, v.nx_q + row + 16 * b, v.nx_s + b16 + b, v.nx_c + b16 + b);
+                    quant_elem16(iv, ok, v.in_q + row + 16 * b, v.in_s + b16 + b, v.in_c + b16 + b);
+                } else if (ok) { v.nx_f[row + i] = nv; v.in_f[row + i] = iv; }
+                if (ok) {
+                    if (rows_f) rows_f[row + i] = iv;
+                    v.rin[row + i] = __fmul_rn(__fmul_rn(xs, d.inv_sqrt_e), rs[k]);
+                }
+            }
+        }
+        return;
+    }
     const float scale = rms_scale_from(sumsq256(xt, E, sh), E, d.eps);
     if (FA) {
         const size_t b16 = (size_t)t * (E / 16);
         quant_row(E, v.nx_q + (size_t)t * E, v.nx_s + b16, v.nx_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.ffn_norm + i)); });
         quant_row(E, v.in_q + (size_t)t * E, v.in_s + b16, v.in_c + b16, [&](int i) { return __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i)); });
         if (rows_f)                                             /* the routed experts' input as fp32 rows (expert-parallel dispatch) */
-            for (int i = threadIdx.x; i < E; i += 256) rows_f[(size_t)t * E + i] = __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i));
+            for (int i = tid; i < E; i += 256) rows_f[(size_t)t * E + i] = __fmul_rn(__fmul_rn(xt[i], scale), __ldg(L.pre_ffw2 + i));
     } else {
-        for (int i = threadIdx.x; i < E; i += 256) {
+        for (int i = tid; i < E; i += 256) {
             const float xs = __fmul_rn(xt[i], scale);
             v.nx_f[(size_t)t * E + i] = __fmul_rn(xs, __ldg(L.ffn_norm + i));
             const float iv = __fmul_rn(xs, __ldg(L.pre_ffw2 + i));
@@ -143,7 +196,7 @@ __global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const fl
             if (rows_f) rows_f[(size_t)t * E + i] = iv;
         }
     }
-    for (int i = threadIdx.x; i < E; i += 256)
+    for (int i = tid; i < E; i += 256)
         v.rin[(size_t)t * E + i] = __fmul_rn(__fmul_rn(__fmul_rn(xt[i], scale), d.inv_sqrt_e), __ldg(L.router_scale + i));
 }
 
@@ -202,6 +255,52 @@ __global__ void __launch_bounds__(256) k_b_router(SpDims d, SpLayerDev L, BView 
             if (lane == 0 && e < d.NE && t < M)
                 v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, __ldg(L.router_bias + e)) : r;
         }
+}
+
+/* The same logits for a handful of tokens: one block per expert, so that NE blocks share the router
+ * matrix between them instead of NE/16 (a batch this small is bound by the latency of one block's
+ * loop, not by arithmetic). The expert's row is staged in shared memory; warp w takes tokens w, w+8, ...
+ * four at a time, every (expert, token) chain in the order given above. */
+__global__ void __launch_bounds__(256) k_b_router_small(SpDims d, SpLayerDev L, BView v, int M) {
+    extern __shared__ __align__(16) float4 rw[];               /* [E/4] */
+    const int E = d.E, G = E >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, e = blockIdx.x;
+    const float4 *wrow = reinterpret_cast<const float4 *>(L.router_w + (size_t)e * E);
+    for (int g = threadIdx.x; g < G; g += 256) rw[g] = __ldg(wrow + g);
+    __syncthreads();
+    const float bias = L.router_bias ? __ldg(L.router_bias + e) : 0.0f;
+    for (int t0 = warp; t0 < M; t0 += 32) {
+        const float4 *x[4]; float acc[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int t = t0 + 8 * j;
+            x[j] = reinterpret_cast<const float4 *>(v.rin + (size_t)(t < M ? t : t0) * E);
+            acc[j] = 0.0f;
+        }
+#pragma unroll 4
+        for (int g = lane; g < G; g += 32) {
+            const float4 w = rw[g];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float4 xv = x[j][g];
+                float a = acc[j];
+                a = __fmaf_rn(w.x, xv.x, a); a = __fmaf_rn(w.y, xv.y, a);
+                a = __fmaf_rn(w.z, xv.z, a); a = __fmaf_rn(w.w, xv.w, a);
+                acc[j] = a;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float r = warp_tree(acc[j]);
+            const int t = t0 + 8 * j;
+            if (lane == 0 && t < M) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, bias) : r;
+        }
+    }
+}
+constexpr int kRouterSmallM = 64;
+void launch_router(const SpDims &d, const SpLayerDev &L, BView &v, int M, cudaStream_t st, int *nl) {
+    if (M <= kRouterSmallM && (size_t)d.E * 4 <= 48 * 1024) k_b_router_small<<<d.NE, 256, (size_t)d.E * 4, st>>>(d, L, v, M);
+    else k_b_router<<<dim3((d.NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M);
+    (*nl)++;
 }
 
 /* ---------------------------------------------------------------- K3: moe_topk_host (CF:6220-6240) + bucketing by expert (CF:8594-8624) */
@@ -265,6 +364,18 @@ __global__ void __launch_bounds__(256) k_b_topk(SpDims d, SpLayerDev L, BView v,
 __global__ void __launch_bounds__(256) k_b_quant_rows(const float *x, int n, signed char *q, float *sx, int *corr) {
     const size_t r = blockIdx.x;
     const float *xr = x + r * n;
+    if (n <= 256 * kPrepK) {                                    /* all of the row's loads first, then the dependent steps */
+        float v[kPrepK];
+#pragma unroll
+        for (int k = 0; k < kPrepK; k++) { const int i = (int)threadIdx.x + 256 * k; v[k] = i < n ? xr[i] : 0.0f; }
+#pragma unroll
+        for (int k = 0; k < kPrepK; k++)
+            if (256 * k < n) {
+                const int i = (int)threadIdx.x + 256 * k, b = i >> 4;
+                quant_elem16(v[k], i < n, q + r * n + 16 * b, sx + r * (n / 16) + b, corr + r * (n / 16) + b);
+            }
+        return;
+    }
     quant_row(n, q + r * n, sx + r * (n / 16), corr + r * (n / 16), [&](int i) { return xr[i]; });
 }
 
@@ -390,8 +501,213 @@ __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     }
 }
 
+/* ---------------------------------------------------------------- K4/K6 on the tensor cores (integer flavour)
+ * The same sums as dot_a, bit for bit, with the 16-weight block dots taken by mma.sync m16n8k32
+ * (s8 x s8 -> s32) instead of dp4a chains. A warp owns 16 weight rows. Four chunks (4 x 32 weights)
+ * go through four MMAs that accumulate into one C tile: the activation operand of MMA i is non-zero
+ * only in the column (chunk, half) its k-slots belong to, so column 2q+h of C ends up holding the
+ * integer dot of half h of chunk 4j+q, and lane (g, q) of the warp reads the two block sums of
+ * "its" chunk for rows g and g+8 straight out of its C registers. Lane (g, q) therefore plays the
+ * part that lane (4j+q) % 32 plays in dot_a: it keeps one fp32 accumulator per slot and adds its
+ * chunks in ascending order; the 32 slots of a row are then added in the pairing of warp_tree.
+ *   A operand: code nibbles moved to the top of a byte (value 16*code as s8, no +8 bias, no
+ *              correction term); low nibbles feed k-slots 4q..4q+3, high nibbles 16+4q..16+4q+3.
+ *   B operand: the activations' int8 values; the quantiser already stores every 8 of them as
+ *              4 even-index then 4 odd-index bytes, which is the order the nibble split needs.
+ *   C starts at 0x4B400000 (1.5 * 2^23): the s32 result read as a float is 12582912 + 16*S, and one
+ *              fma by 1/16 gives float(S) exactly, without an integer-to-float conversion.
+ * KS = warps per 16-row unit: 1 (in <= 768: a warp covers the whole row) or 4 (in <= 3072: warp wq
+ * covers slots 8wq..8wq+7 and the slot sums meet in shared memory). */
+constexpr int kMmaTB = 4, kMmaG = 6, kMmaPartStride = 33;
+constexpr int kMmaMagic = 0x4B400000;
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float magic_to_float(int c) { return __fmaf_rn(__int_as_float(c), 0.0625f, -786432.0f); }
+/* the 32 slot sums of one row, added in warp_tree's pairing */
+__device__ __forceinline__ float slot_tree(const float *p) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = p[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < o; i++) v[i] += v[i + o];
+    return v[0];
+}
+
+template <int KS>
+constexpr size_t mma_smem_bytes(int in) {
+    return 16 + (size_t)kMmaTB * in + (size_t)kMmaTB * (in / 16) * 4 + kMmaTB * 4
+         + (KS == 4 ? (size_t)2 * kMmaTB * 16 * kMmaPartStride * 4 : (size_t)8 * kMmaTB * 16 * 4);
+}
+
+template <bool PAIR, int KS>
+__global__ void __launch_bounds__(256, 2) k_b_rows_mma(GroupArgs g) {
+    constexpr int TB = kMmaTB, UNITS = 8 / KS, TPC = PAIR ? UNITS / 2 : UNITS, NACC = KS == 4 ? 2 : 8;
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
+    const int grp = blockIdx.y;
+    int first = 0, cnt;
+    if (g.offset) {
+        int last = g.offset[grp + 1];
+        first = g.offset[grp];
+        first = first < 0 ? 0 : (first > g.M ? g.M : first);
+        last = last > g.M ? g.M : last;
+        cnt = last - first;
+    } else cnt = g.count ? g.count[grp] : g.M;
+    if (cnt <= 0) return;
+    const int in = g.in, n32 = in >> 5, b16 = in >> 4, ngroups = (n32 + 3) >> 2;
+    unsigned char *zero = sm;                                   /* 16 zero bytes: the B operand of a column that is not this lane's */
+    unsigned char *P = sm + 16;                                 /* [TB][in] activations, as the quantiser stored them */
+    float *sxs = reinterpret_cast<float *>(P + (size_t)TB * in);/* [TB][in/16] activation block scales */
+    int *items = reinterpret_cast<int *>(sxs + (size_t)TB * b16);
+    float *part = reinterpret_cast<float *>(items + TB);        /* KS=4: [2][TB][16][33] slot sums; KS=1: [8][TB][16] row sums */
+    const int unit = warp / KS, wq = warp % KS;
+    const int tile = blockIdx.x * TPC + (PAIR ? unit >> 1 : unit);
+    const bool up = PAIR && (unit & 1);
+    const bool tile_ok = tile * 16 < g.rows;
+    const int r0 = tile_ok ? tile * 16 : 0;                     /* a warp past the last tile keeps valid pointers and computes nothing */
+    const size_t rb = (size_t)in / 2;
+    const size_t row = (size_t)grp * g.rows_per_group + r0 + gq + (up && !g.ucodes ? g.up_off : 0);
+    const uint8_t *codes0 = (up && g.ucodes ? g.ucodes : g.codes) + row * rb, *codes1 = codes0 + 8 * rb;
+    const uint16_t *bs0 = (up && g.ucodes ? g.ubs : g.bs) + row * n32, *bs1 = bs0 + 8 * (size_t)n32;
+    const int *list = g.list ? g.list + (size_t)grp * g.list_stride : nullptr;
+    const bool bvalid = (gq >> 1) == q;                         /* this lane's k-slots belong to column pair (2q, 2q+1) */
+    const int bh = gq & 1;
+    if (tid < 4) reinterpret_cast<int *>(zero)[tid] = 0;
+
+    for (int b0 = blockIdx.z * TB; b0 < cnt; b0 += gridDim.z * TB) {   /* token batches are dealt round-robin over grid.z */
+        const int nb = cnt - b0 < TB ? cnt - b0 : TB;
+        __syncthreads();                                        /* the previous batch's readers are done */
+        if (tid < nb) items[tid] = list ? list[b0 + tid] : (g.index ? g.index[first + b0 + tid] : first + b0 + tid);
+        __syncthreads();
+        const int w16 = in >> 4;                                /* the activations are already stored even/odd split per 8 (quant_elem16) */
+        for (int w = tid; w < nb * w16; w += 256) {
+            const int t = w / w16, k = w - t * w16;
+            reinterpret_cast<int4 *>(P + (size_t)t * in)[k] = reinterpret_cast<const int4 *>(g.q + (size_t)(items[t] / g.act_div) * in)[k];
+        }
+        for (int w = tid; w < nb * b16; w += 256) {
+            const int t = w / b16, k = w - t * b16;
+            sxs[t * b16 + k] = g.sx[(size_t)(items[t] / g.act_div) * b16 + k];
+        }
+        __syncthreads();
+
+        if (tile_ok) {
+            float acc[TB][NACC][2];
+#pragma unroll
+            for (int t = 0; t < TB; t++)
+#pragma unroll
+                for (int a = 0; a < NACC; a++) acc[t][a][0] = acc[t][a][1] = 0.0f;
+#pragma unroll
+            for (int jj = 0; jj < kMmaG; jj++) {
+                const int j = KS == 4 ? 8 * (jj >> 1) + 2 * wq + (jj & 1) : jj;
+                if (j < ngroups) {
+                    const int ai = KS == 4 ? (jj & 1) : jj;
+                    const int c = 4 * j + q;
+                    const bool cv = c < n32;
+                    const int cc = cv ? c : n32 - 1;                    /* every lane loads; a lane past the row's end reads the last chunk and drops it */
+                    int4 w0 = ld_stream16(codes0 + 16 * (size_t)cc), w1 = ld_stream16(codes1 + 16 * (size_t)cc);
+                    const float s0 = h2f(ld_stream_u16(bs0 + cc)), s1 = h2f(ld_stream_u16(bs1 + cc));
+                    if (!cv) { w0 = make_int4(0, 0, 0, 0); w1 = w0; }
+                    const unsigned x0[4] = {(unsigned)w0.x, (unsigned)w0.y, (unsigned)w0.z, (unsigned)w0.w};
+                    const unsigned x1[4] = {(unsigned)w1.x, (unsigned)w1.y, (unsigned)w1.z, (unsigned)w1.w};
+                    unsigned a[4][4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        a[i][0] = (x0[i] << 4) & 0xF0F0F0F0u; a[i][1] = (x1[i] << 4) & 0xF0F0F0F0u;
+                        a[i][2] = x0[i] & 0xF0F0F0F0u;        a[i][3] = x1[i] & 0xF0F0F0F0u;
+                    }
+                    const int boff = c * 32 + bh * 16;
+#pragma unroll
+                    for (int t = 0; t < TB; t++) {
+                        if (t < nb) {
+                            const unsigned char *src = bvalid && cv ? P + (size_t)t * in + boff : zero;
+                            const uint4 l0 = *reinterpret_cast<const uint4 *>(bh == 0 ? src : zero);
+                            const uint4 l1 = *reinterpret_cast<const uint4 *>(bh == 1 ? src : zero);
+                            int ca[4] = {kMmaMagic, kMmaMagic, kMmaMagic, kMmaMagic}, cb[4] = {kMmaMagic, kMmaMagic, kMmaMagic, kMmaMagic};
+                            mma_s8(ca, a[0][0], a[0][1], a[0][2], a[0][3], l0.x, l0.y);
+                            mma_s8(cb, a[2][0], a[2][1], a[2][2], a[2][3], l1.x, l1.y);
+                            mma_s8(ca, a[1][0], a[1][1], a[1][2], a[1][3], l0.z, l0.w);
+                            mma_s8(cb, a[3][0], a[3][1], a[3][2], a[3][3], l1.z, l1.w);
+                            if (cv) {
+                                const float2 s2 = *reinterpret_cast<const float2 *>(sxs + t * b16 + 2 * c);
+                                acc[t][ai][0] = __fmaf_rn(s0, __fmaf_rn(magic_to_float(ca[0]), s2.x, __fmul_rn(magic_to_float(cb[1]), s2.y)), acc[t][ai][0]);
+                                acc[t][ai][1] = __fmaf_rn(s1, __fmaf_rn(magic_to_float(ca[2]), s2.x, __fmul_rn(magic_to_float(cb[3]), s2.y)), acc[t][ai][1]);
+                            }
+                        }
+                    }
+                }
+            }
+            if (KS == 4) {
+#pragma unroll
+                for (int t = 0; t < TB; t++)
+                    if (t < nb)
+#pragma unroll
+                        for (int a2 = 0; a2 < NACC; a2++)
+#pragma unroll
+                            for (int r = 0; r < 2; r++)
+                                part[((size_t)(unit * TB + t) * 16 + gq + 8 * r) * kMmaPartStride + 8 * wq + 4 * a2 + q] = acc[t][a2][r];
+            } else {
+#pragma unroll
+                for (int t = 0; t < TB; t++)
+                    if (t < nb)
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            float v[8];
+#pragma unroll
+                            for (int a2 = 0; a2 < 8; a2++) v[a2] = acc[t][a2][r];
+#pragma unroll
+                            for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+                                for (int i = 0; i < o; i++) v[i] += v[i + o];      /* slots s+16, s+8, s+4 sit in this lane */
+                            float s = v[0];
+                            s += __shfl_down_sync(0xffffffffu, s, 2);
+                            s += __shfl_down_sync(0xffffffffu, s, 1);
+                            if (q == 0) part[(size_t)(unit * TB + t) * 16 + gq + 8 * r] = s;
+                        }
+            }
+        }
+        __syncthreads();
+        for (int w = tid; w < TPC * nb * 16; w += 256) {
+            const int tl = w / (nb * 16), rem = w - tl * (nb * 16), t = rem >> 4, row = rem & 15;
+            const int r = (blockIdx.x * TPC + tl) * 16 + row;
+            if (r < g.rows) {
+                const int u0 = PAIR ? 2 * tl : tl;
+                float o;
+                if (KS == 4) {
+                    o = slot_tree(part + ((size_t)(u0 * TB + t) * 16 + row) * kMmaPartStride);
+                    if (PAIR) o = gelu_mul(o, slot_tree(part + ((size_t)((u0 + 1) * TB + t) * 16 + row) * kMmaPartStride));
+                } else {
+                    o = part[(size_t)(u0 * TB + t) * 16 + row];
+                    if (PAIR) o = gelu_mul(o, part[(size_t)((u0 + 1) * TB + t) * 16 + row]);
+                }
+                g.out[(size_t)items[t] * g.out_stride + r] = o;
+            }
+        }
+    }
+}
+
 template <bool FA, bool PAIR>
 void launch_rows(const GroupArgs &g, int groups, cudaStream_t st, int *nl) {
+    if (FA && (g.rows & 15) == 0 && (g.in & 31) == 0 && g.in <= 3072) {
+        const int tiles = g.rows / 16;
+        /* one group holding every token (the shared expert) spreads its token batches over grid.z; routed
+         * groups hold M*NU/groups tokens on average, so two CTAs per tile cover the long lists */
+        const int batches = (g.M + kMmaTB - 1) / kMmaTB;
+        const unsigned z = (unsigned)(groups == 1 ? (batches < 32 ? batches : 32) : (batches > 2 ? 2 : 1));
+        if (g.in <= 768) {
+            const int tpc = PAIR ? 4 : 8;
+            k_b_rows_mma<PAIR, 1><<<dim3((unsigned)((tiles + tpc - 1) / tpc), (unsigned)groups, z), 256, mma_smem_bytes<1>(g.in), st>>>(g);
+        } else {
+            const int tpc = PAIR ? 1 : 2;
+            k_b_rows_mma<PAIR, 4><<<dim3((unsigned)((tiles + tpc - 1) / tpc), (unsigned)groups, z), 256, mma_smem_bytes<4>(g.in), st>>>(g);
+        }
+        (*nl)++;
+        return;
+    }
     const dim3 grid((unsigned)((g.rows + 7) / 8), (unsigned)groups);
     const int nit = ((g.in >> 5) + 31) >> 5;
     if (nit <= 1) k_b_rows<FA, PAIR, 1><<<grid, 256, 0, st>>>(g);
@@ -440,9 +756,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
                       BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, NU = d.NU, FFE = d.FFE, FFS = d.FFS;
     k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, nullptr); (*nl)++;
-    {
-        k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
-    }
+    launch_router(d, L, v, M, st, nl);
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
     if (!FA && tc) {                                            /* prefill arithmetic on the tensor cores */
         cudaError_t e = sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
@@ -590,7 +904,7 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
     const int E = d.E, NE = d.NE, NU = d.NU;
     k_b_prep<FA><<<M, 256, 0, st>>>(d, L, x, v, FA ? v.in_f : nullptr); (*nl)++;
     cudaError_t e = cudaSuccess;
-    k_b_router<<<dim3((NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M); (*nl)++;
+    launch_router(d, L, v, M, st, nl);
     k_b_topk<<<M, 256, (size_t)NE * 12, st>>>(d, L, v, M, sel, wts, status); (*nl)++;
     /* the send buffer: rows sorted by expert (so also by owner), ready for the all-to-all */
     k_b_scan<<<1, 1024, 0, st>>>(v.count, NE, v.ep_off); (*nl)++;

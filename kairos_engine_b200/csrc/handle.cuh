@@ -36,6 +36,7 @@ struct sp_moe {
     SpGraphScratch gs; unsigned char *gs_base; float *g_x, *g_y; int32_t *g_sel; float *g_wts;
     int decode_impl;            /* 0 = rows staged through shared memory (decode_staged.cu), 1 = rows read directly (decode_graph.cu) */
     unsigned staged_flags;
+    int seq_tokens;                       /* decode batches up to this size run token by token through the single-token graph */
     long long *stamps;          /* device time stamps of the last layer of a decode run (SP_MOE_TIMING=1), else NULL */
     long long *stamps_host;
     uint64_t timing_runs; double timing_us[3][4], timing_layer_us;

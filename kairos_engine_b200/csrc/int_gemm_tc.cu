@@ -10,13 +10,14 @@
  * A is [M][K], B is [N][K] (the tiled kernels' layout); K a multiple of 16.
  * Warp roles: 0-3 epilogue, 4 TMA, 5 MMA issue + TMEM allocation. Every wait is bounded.
  */
+#include <mutex>
 #include "tc_common.cuh"
 #include "../../include/sp_engine/moe_backend.h"
 
 namespace {
 using namespace sp_tc;
 
-constexpr int kTM = 128, kTN = 256, kBKB = 128, kStages = 4, kThreads = 192;
+constexpr int kTM = 128, kTN = 256, kBKB = 128, kStages = 4, kThreads = 192, kMaxDevices = 64;
 constexpr uint32_t kABytes = kTM * 128, kBBytes = kTN * 128, kStageBytes = kABytes + kBBytes;   /* 16 KB + 32 KB */
 constexpr uint32_t kBarOff = kStages * kStageBytes, kSmemBytes = kBarOff + 192 + 1024;
 
@@ -163,7 +164,7 @@ cudaError_t make_u8_map(EncodeTiledFn fn, CUtensorMap *m, const void *ptr, int K
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-int run_q8(const int8_t *A, const int8_t *B, const float *sa, const float *sb, uint16_t *C, int M, int K, int N, cudaStream_t st, const char *who) {
+int run_q8(const int8_t *A, const int8_t *B, const float *sa, const float *sb, uint16_t *C, int M, int K, int N, cudaStream_t st, const char *who, int **status_out = nullptr) {
     if (!A || !B || !sa || !sb || !C) return ig_fail(SP_MOE_EBADARG, "quantised GEMM: NULL argument");
     if (M <= 0 || N <= 0 || K <= 0 || (K & 15)) return ig_fail(SP_MOE_EBADARG, "quantised GEMM: M, N, K must be positive and K a multiple of 16");
     if (((uintptr_t)A | (uintptr_t)B) & 15) return ig_fail(SP_MOE_EBADARG, "quantised GEMM: operand pointers must be 16-byte aligned");
@@ -174,14 +175,34 @@ int run_q8(const int8_t *A, const int8_t *B, const float *sa, const float *sb, u
     IgMaps maps;
     if (make_u8_map(fn, &maps.a, A, K, M, kTM) != cudaSuccess || make_u8_map(fn, &maps.b, B, K, N, kTN) != cudaSuccess)
         return ig_fail(SP_MOE_EBADARG, "quantised GEMM: could not describe the operands to the TMA unit");
-    static int *status = nullptr;                         /* one error word per process, allocated at first use */
-    if (!status) { if (cudaMalloc((void **)&status, 256) != cudaSuccess || cudaMemset(status, 0, 256) != cudaSuccess) return ig_fail(SP_MOE_ECUDA, "quantised GEMM: status word allocation failed"); }
-    static bool attr = false;
-    if (!attr) { if (cudaFuncSetAttribute(k_i8_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return ig_fail(SP_MOE_ECUDA, "quantised GEMM: shared-memory attribute"); attr = true; }
+    static std::mutex mu;                                 /* one error word and one attribute call per device, at first use there */
+    static int *status_of[kMaxDevices] = {};
+    if (dev < 0 || dev >= kMaxDevices) return ig_fail(SP_MOE_EUNSUPPORTED, "quantised GEMM: device ordinal out of range");
+    int *status = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!status_of[dev]) {
+            int *p = nullptr;
+            if (cudaFuncSetAttribute(k_i8_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return ig_fail(SP_MOE_ECUDA, "quantised GEMM: shared-memory attribute");
+            if (cudaMalloc((void **)&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) { if (p) cudaFree(p); return ig_fail(SP_MOE_ECUDA, "quantised GEMM: status word allocation failed"); }
+            status_of[dev] = p;
+        }
+        status = status_of[dev];
+    }
     const int tiles = ((M + kTM - 1) / kTM) * ((N + kTN - 1) / kTN);
     k_i8_gemm<<<tiles < sms ? tiles : sms, kThreads, kSmemBytes, st>>>(maps, sa, sb, reinterpret_cast<__half *>(C), M, K, N, status);
     (void)who;
-    return cudaGetLastError() == cudaSuccess ? SP_MOE_OK : ig_fail(SP_MOE_ECUDA, "quantised GEMM: kernel launch failed");
+    if (cudaGetLastError() != cudaSuccess) return ig_fail(SP_MOE_ECUDA, "quantised GEMM: kernel launch failed");
+    if (status_out) *status_out = status;
+    return SP_MOE_OK;
+}
+
+/* After the stream has drained: a bounded wait that ran out inside the kernel left a non-zero word. */
+int read_status(int *status) {
+    int v = 0;
+    if (cudaMemcpy(&v, status, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return ig_fail(SP_MOE_ECUDA, "quantised GEMM: status read failed");
+    if (v) { cudaMemset(status, 0, sizeof v); return ig_fail(SP_MOE_ECUDA, "quantised GEMM: a bounded wait inside the kernel ran out"); }
+    return SP_MOE_OK;
 }
 
 }  // namespace
@@ -194,7 +215,7 @@ extern "C" int sp_frob_matmul_q8_dev(const int8_t *A_dev, const int8_t *B_dev, c
 extern "C" int sp_frob_matmul_q4_dev(const uint8_t *A_q4_dev, const uint8_t *B_q4_dev, const float *scale_a_dev, const float *scale_b_dev,
                                      uint16_t *C_f16_dev, int M, int K, int N, void *stream) {
     if (!A_q4_dev || !B_q4_dev) return ig_fail(SP_MOE_EBADARG, "sp_frob_matmul_q4_dev: NULL argument");
-    if (K <= 0 || (K & 15)) return ig_fail(SP_MOE_EBADARG, "sp_frob_matmul_q4_dev: K must be a positive multiple of 16");
+    if (M <= 0 || N <= 0 || K <= 0 || (K & 15)) return ig_fail(SP_MOE_EBADARG, "sp_frob_matmul_q4_dev: M, N, K must be positive and K a multiple of 16");
     cudaStream_t st = (cudaStream_t)stream;
     int8_t *a8 = nullptr, *b8 = nullptr;
     if (cudaMalloc((void **)&a8, (size_t)M * K) != cudaSuccess || cudaMalloc((void **)&b8, (size_t)N * K) != cudaSuccess) {
@@ -204,8 +225,11 @@ extern "C" int sp_frob_matmul_q4_dev(const uint8_t *A_q4_dev, const uint8_t *B_q
     }
     k_unpack_s4<<<1024, 256, 0, st>>>(A_q4_dev, a8, (size_t)M * K / 2);
     k_unpack_s4<<<1024, 256, 0, st>>>(B_q4_dev, b8, (size_t)N * K / 2);
-    int rc = run_q8(a8, b8, scale_a_dev, scale_b_dev, C_f16_dev, M, K, N, st, "sp_frob_matmul_q4_dev");
-    cudaStreamSynchronize(st);
+    int *status = nullptr;
+    int rc = run_q8(a8, b8, scale_a_dev, scale_b_dev, C_f16_dev, M, K, N, st, "sp_frob_matmul_q4_dev", &status);
+    const cudaError_t se = cudaStreamSynchronize(st);      /* the scratch is freed below, so the stream is drained here anyway */
     cudaFree(a8); cudaFree(b8);
+    if (rc == SP_MOE_OK && se != cudaSuccess) rc = ig_fail(SP_MOE_ECUDA, "sp_frob_matmul_q4_dev: the stream reported an error");
+    if (rc == SP_MOE_OK) rc = read_status(status);
     return rc;
 }
