@@ -538,10 +538,21 @@ __device__ __forceinline__ float slot_tree(const float *p) {
     return v[0];
 }
 
+/* shared-memory row stride of the staged codes: the two rows a quarter-warp reads (64 B each) must fall in different banks */
+__host__ __device__ constexpr int mma_a_stride(int in) { return in / 2 + ((64 - (in / 2) % 128 + 128) % 128); }
 template <int KS>
 constexpr size_t mma_smem_bytes(int in) {
-    return 16 + (size_t)kMmaTB * in + (size_t)kMmaTB * (in / 16) * 4 + kMmaTB * 4
-         + (KS == 4 ? (size_t)2 * kMmaTB * 16 * kMmaPartStride * 4 : (size_t)8 * kMmaTB * 16 * 4);
+    return (size_t)kMmaTB * (in + 16) + (size_t)kMmaTB * (in / 16) * 4 + 16
+         + (KS == 4 ? (size_t)2 * kMmaTB * 16 * kMmaPartStride * 4 : (size_t)8 * kMmaTB * 16 * 4)
+         + (size_t)(8 / KS) * 16 * mma_a_stride(in);
+}
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src) : "memory");
+}
+/* D = A*B + {c, c, c, c}: the first MMA of a chain reads its start value from one register */
+__device__ __forceinline__ void mma_s8_first(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1, int c) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
 }
 
 template <bool PAIR, int KS>
@@ -558,41 +569,74 @@ __global__ void __launch_bounds__(256, 2) k_b_rows_mma(GroupArgs g) {
         last = last > g.M ? g.M : last;
         cnt = last - first;
     } else cnt = g.count ? g.count[grp] : g.M;
-    if (cnt <= 0) return;
-    const int in = g.in, n32 = in >> 5, b16 = in >> 4, ngroups = (n32 + 3) >> 2;
-    unsigned char *zero = sm;                                   /* 16 zero bytes: the B operand of a column that is not this lane's */
-    unsigned char *P = sm + 16;                                 /* [TB][in] activations, as the quantiser stored them */
-    float *sxs = reinterpret_cast<float *>(P + (size_t)TB * in);/* [TB][in/16] activation block scales */
-    int *items = reinterpret_cast<int *>(sxs + (size_t)TB * b16);
-    float *part = reinterpret_cast<float *>(items + TB);        /* KS=4: [2][TB][16][33] slot sums; KS=1: [8][TB][16] row sums */
+    if ((int)blockIdx.z * TB >= cnt) return;
+    const int in = g.in, n32 = in >> 5, b16 = in >> 4, ngroups = (n32 + 3) >> 2, astride = mma_a_stride(in), pstride = in + 16;
+    unsigned char *P = sm;                                      /* [TB][in + 16]: a token's activations as the quantiser stored them, then 16 zero bytes */
+    float *sxs = reinterpret_cast<float *>(P + (size_t)TB * pstride);   /* [TB][in/16] activation block scales */
+    int *items = reinterpret_cast<int *>(sxs + (size_t)TB * b16);      /* [TB] (+ padding to 16 bytes) */
+    float *part = reinterpret_cast<float *>(items + 4);         /* KS=4: [2][TB][16][33] slot sums; KS=1: [8][TB][16] row sums */
+    unsigned char *A = reinterpret_cast<unsigned char *>(part + (KS == 4 ? 2 * TB * 16 * kMmaPartStride : 8 * TB * 16));   /* [UNITS][16][astride] codes */
+    const size_t rb = (size_t)in / 2;
+
+    /* the block's weight rows go to shared memory once, in one burst: warp w copies rows w, w+8, ... */
+    {
+        const int ppr = (int)(rb >> 4);
+        for (int ur = warp; ur < UNITS * 16; ur += 8) {
+            const int u = ur >> 4, r = ur & 15;
+            const int tile_u = blockIdx.x * TPC + (PAIR ? u >> 1 : u);
+            if (tile_u * 16 < g.rows) {
+                const bool up_u = PAIR && (u & 1);
+                const size_t row = (size_t)grp * g.rows_per_group + tile_u * 16 + r + (up_u && !g.ucodes ? g.up_off : 0);
+                const uint8_t *src = (up_u && g.ucodes ? g.ucodes : g.codes) + row * rb;
+                unsigned char *dst = A + (size_t)ur * astride;
+                for (int k = lane; k < ppr; k += 32) cp_async16(dst + 16 * k, src + 16 * (size_t)k);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     const int unit = warp / KS, wq = warp % KS;
     const int tile = blockIdx.x * TPC + (PAIR ? unit >> 1 : unit);
     const bool up = PAIR && (unit & 1);
     const bool tile_ok = tile * 16 < g.rows;
     const int r0 = tile_ok ? tile * 16 : 0;                     /* a warp past the last tile keeps valid pointers and computes nothing */
-    const size_t rb = (size_t)in / 2;
-    const size_t row = (size_t)grp * g.rows_per_group + r0 + gq + (up && !g.ucodes ? g.up_off : 0);
-    const uint8_t *codes0 = (up && g.ucodes ? g.ucodes : g.codes) + row * rb, *codes1 = codes0 + 8 * rb;
-    const uint16_t *bs0 = (up && g.ucodes ? g.ubs : g.bs) + row * n32, *bs1 = bs0 + 8 * (size_t)n32;
+    const unsigned char *A0 = A + ((size_t)unit * 16 + gq) * astride, *A1 = A0 + 8 * (size_t)astride;
+    float sc[kMmaG][2];                                         /* this lane's block scales: rows gq and gq+8, one chunk per group */
+    {
+        const size_t row = (size_t)grp * g.rows_per_group + r0 + gq + (up && !g.ucodes ? g.up_off : 0);
+        const uint16_t *bs0 = (up && g.ucodes ? g.ubs : g.bs) + row * n32, *bs1 = bs0 + 8 * (size_t)n32;
+#pragma unroll
+        for (int jj = 0; jj < kMmaG; jj++) {
+            const int j = KS == 4 ? 8 * (jj >> 1) + 2 * wq + (jj & 1) : jj;
+            const int c = 4 * j + q, cc = c < n32 ? c : n32 - 1;
+            sc[jj][0] = h2f(ld_stream_u16(bs0 + cc)); sc[jj][1] = h2f(ld_stream_u16(bs1 + cc));
+        }
+    }
     const int *list = g.list ? g.list + (size_t)grp * g.list_stride : nullptr;
     const bool bvalid = (gq >> 1) == q;                         /* this lane's k-slots belong to column pair (2q, 2q+1) */
     const int bh = gq & 1;
-    if (tid < 4) reinterpret_cast<int *>(zero)[tid] = 0;
+    if (tid < 4 * TB) reinterpret_cast<int *>(P + (size_t)(tid >> 2) * pstride + in)[tid & 3] = 0;
+    const bool vec_sx = (b16 & 3) == 0;                         /* 16-byte copies of the scales need 16-byte rows */
 
     for (int b0 = blockIdx.z * TB; b0 < cnt; b0 += gridDim.z * TB) {   /* token batches are dealt round-robin over grid.z */
         const int nb = cnt - b0 < TB ? cnt - b0 : TB;
         __syncthreads();                                        /* the previous batch's readers are done */
-        if (tid < nb) items[tid] = list ? list[b0 + tid] : (g.index ? g.index[first + b0 + tid] : first + b0 + tid);
-        __syncthreads();
-        const int w16 = in >> 4;                                /* the activations are already stored even/odd split per 8 (quant_elem16) */
-        for (int w = tid; w < nb * w16; w += 256) {
-            const int t = w / w16, k = w - t * w16;
-            reinterpret_cast<int4 *>(P + (size_t)t * in)[k] = reinterpret_cast<const int4 *>(g.q + (size_t)(items[t] / g.act_div) * in)[k];
+        /* warps 2t and 2t+1 fetch token t: its int8 row and its block scales */
+        {
+            const int t = warp >> 1, hw = warp & 1;
+            if (t < nb) {
+                const int item = list ? list[b0 + t] : (g.index ? g.index[first + b0 + t] : first + b0 + t);
+                if (hw == 0 && lane == 0) items[t] = item;
+                const size_t arow = (size_t)(item / g.act_div);
+                const signed char *qs = g.q + arow * in;
+                unsigned char *pd = P + (size_t)t * pstride;
+                for (int k = lane + 32 * hw; k < b16; k += 64) cp_async16(pd + 16 * k, qs + 16 * (size_t)k);
+                const float *ss = g.sx + arow * b16;
+                if (vec_sx) { for (int k = lane + 32 * hw; k < (b16 >> 2); k += 64) cp_async16(sxs + t * b16 + 4 * k, ss + 4 * k); }
+                else { for (int k = lane + 32 * hw; k < b16; k += 64) sxs[t * b16 + k] = ss[k]; }
+            }
         }
-        for (int w = tid; w < nb * b16; w += 256) {
-            const int t = w / b16, k = w - t * b16;
-            sxs[t * b16 + k] = g.sx[(size_t)(items[t] / g.act_div) * b16 + k];
-        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
 
         if (tile_ok) {
@@ -608,28 +652,29 @@ __global__ void __launch_bounds__(256, 2) k_b_rows_mma(GroupArgs g) {
                     const int ai = KS == 4 ? (jj & 1) : jj;
                     const int c = 4 * j + q;
                     const bool cv = c < n32;
-                    const int cc = cv ? c : n32 - 1;                    /* every lane loads; a lane past the row's end reads the last chunk and drops it */
-                    int4 w0 = ld_stream16(codes0 + 16 * (size_t)cc), w1 = ld_stream16(codes1 + 16 * (size_t)cc);
-                    const float s0 = h2f(ld_stream_u16(bs0 + cc)), s1 = h2f(ld_stream_u16(bs1 + cc));
-                    if (!cv) { w0 = make_int4(0, 0, 0, 0); w1 = w0; }
-                    const unsigned x0[4] = {(unsigned)w0.x, (unsigned)w0.y, (unsigned)w0.z, (unsigned)w0.w};
-                    const unsigned x1[4] = {(unsigned)w1.x, (unsigned)w1.y, (unsigned)w1.z, (unsigned)w1.w};
+                    const int cc = cv ? c : n32 - 1;                    /* a lane past the row's end reads the last chunk and drops it */
+                    uint4 w0 = *reinterpret_cast<const uint4 *>(A0 + 16 * cc), w1 = *reinterpret_cast<const uint4 *>(A1 + 16 * cc);
+                    if (!cv) { w0 = make_uint4(0, 0, 0, 0); w1 = w0; }
+                    const float s0 = sc[jj][0], s1 = sc[jj][1];
+                    const unsigned x0[4] = {w0.x, w0.y, w0.z, w0.w};
+                    const unsigned x1[4] = {w1.x, w1.y, w1.z, w1.w};
                     unsigned a[4][4];
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         a[i][0] = (x0[i] << 4) & 0xF0F0F0F0u; a[i][1] = (x1[i] << 4) & 0xF0F0F0F0u;
                         a[i][2] = x0[i] & 0xF0F0F0F0u;        a[i][3] = x1[i] & 0xF0F0F0F0u;
                     }
-                    const int boff = c * 32 + bh * 16;
+                    /* a lane whose k-slots are not in column (chunk, half) reads the token's 16 zero bytes */
+                    const int off0 = bvalid && cv && bh == 0 ? c * 32 : in, off1 = bvalid && cv && bh == 1 ? c * 32 + 16 : in;
 #pragma unroll
                     for (int t = 0; t < TB; t++) {
                         if (t < nb) {
-                            const unsigned char *src = bvalid && cv ? P + (size_t)t * in + boff : zero;
-                            const uint4 l0 = *reinterpret_cast<const uint4 *>(bh == 0 ? src : zero);
-                            const uint4 l1 = *reinterpret_cast<const uint4 *>(bh == 1 ? src : zero);
-                            int ca[4] = {kMmaMagic, kMmaMagic, kMmaMagic, kMmaMagic}, cb[4] = {kMmaMagic, kMmaMagic, kMmaMagic, kMmaMagic};
-                            mma_s8(ca, a[0][0], a[0][1], a[0][2], a[0][3], l0.x, l0.y);
-                            mma_s8(cb, a[2][0], a[2][1], a[2][2], a[2][3], l1.x, l1.y);
+                            const unsigned char *pt = P + (size_t)t * pstride;
+                            const uint4 l0 = *reinterpret_cast<const uint4 *>(pt + off0);
+                            const uint4 l1 = *reinterpret_cast<const uint4 *>(pt + off1);
+                            int ca[4], cb[4];
+                            mma_s8_first(ca, a[0][0], a[0][1], a[0][2], a[0][3], l0.x, l0.y, kMmaMagic);
+                            mma_s8_first(cb, a[2][0], a[2][1], a[2][2], a[2][3], l1.x, l1.y, kMmaMagic);
                             mma_s8(ca, a[1][0], a[1][1], a[1][2], a[1][3], l0.z, l0.w);
                             mma_s8(cb, a[3][0], a[3][1], a[3][2], a[3][3], l1.z, l1.w);
                             if (cv) {
@@ -671,23 +716,32 @@ __global__ void __launch_bounds__(256, 2) k_b_rows_mma(GroupArgs g) {
             }
         }
         __syncthreads();
-        for (int w = tid; w < TPC * nb * 16; w += 256) {
-            const int tl = w / (nb * 16), rem = w - tl * (nb * 16), t = rem >> 4, row = rem & 15;
-            const int r = (blockIdx.x * TPC + tl) * 16 + row;
-            if (r < g.rows) {
-                const int u0 = PAIR ? 2 * tl : tl;
-                float o;
-                if (KS == 4) {
-                    o = slot_tree(part + ((size_t)(u0 * TB + t) * 16 + row) * kMmaPartStride);
-                    if (PAIR) o = gelu_mul(o, slot_tree(part + ((size_t)((u0 + 1) * TB + t) * 16 + row) * kMmaPartStride));
-                } else {
-                    o = part[(size_t)(u0 * TB + t) * 16 + row];
-                    if (PAIR) o = gelu_mul(o, part[(size_t)((u0 + 1) * TB + t) * 16 + row]);
-                }
-                g.out[(size_t)items[t] * g.out_stride + r] = o;
+        /* one thread per (unit, token, row); with PAIR the gate thread (even lane) takes the up value from its neighbour */
+        {
+            const int per = nb * 16 * (PAIR ? 2 : 1);           /* threads per tile */
+            for (int w0 = 0; w0 < TPC * per; w0 += 256) {
+                const int w = w0 + tid;
+                const bool act = w < TPC * per;
+                const int tl = act ? w / per : 0, rem = act ? w - tl * per : 0;
+                const int half = PAIR ? rem & 1 : 0, tr = PAIR ? rem >> 1 : rem, t = tr >> 4, row = tr & 15;
+                const int u = PAIR ? 2 * tl + half : tl;
+                float o = 0.0f;
+                if (act) o = KS == 4 ? slot_tree(part + ((size_t)(u * TB + t) * 16 + row) * kMmaPartStride) : part[(size_t)(u * TB + t) * 16 + row];
+                if (PAIR) { const float other = __shfl_down_sync(0xffffffffu, o, 1); if (half == 0) o = gelu_mul(o, other); }
+                const int r = (blockIdx.x * TPC + tl) * 16 + row;
+                if (act && half == 0 && r < g.rows) g.out[(size_t)items[t] * g.out_stride + r] = o;
             }
         }
     }
+}
+/* the staged rows need more than the default 48 KB of shared memory: a per-device setting */
+cudaError_t mma_rows_prepare() {
+    const int lim = 200 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(k_b_rows_mma<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_b_rows_mma<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_b_rows_mma<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_b_rows_mma<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    return e;
 }
 
 template <bool FA, bool PAIR>
@@ -984,7 +1038,9 @@ cudaError_t sp_batched_alloc(const SpDims &d, int max_tokens, int max_rows, SpBa
     s->max_rows = max_rows > max_tokens * d.NU ? max_rows : max_tokens * d.NU;
     s->bytes = blayout(d, max_tokens, s->max_rows, [](int, size_t) {});
     s->tc = nullptr;
-    cudaError_t e = cudaMalloc(&s->base, s->bytes);
+    cudaError_t e = mma_rows_prepare();
+    if (e != cudaSuccess) return e;
+    e = cudaMalloc(&s->base, s->bytes);
     if (e != cudaSuccess) { s->base = nullptr; return e; }
     *bytes = s->bytes;
     /* house convention: behaviour switches are SP_* variables read once. "simt" keeps prefill on the fp32 CUDA-core kernels. */
