@@ -148,7 +148,7 @@ extern "C" int sp_moe_open(const sp_moe_config *cfg, sp_moe **out) {
         const char *fv = getenv("SP_MOE_STAGED_FLAGS");
         h->staged_flags = fv ? (unsigned)strtoul(fv, nullptr, 0) : (unsigned)SP_STAGED_DEFAULT;
         const char *sq = getenv("SP_MOE_SEQ_TOKENS");              /* tuning switch: 1 sends every batch of 2+ tokens to the batched kernels */
-        h->seq_tokens = sq ? atoi(sq) : 8;
+        h->seq_tokens = sq ? atoi(sq) : 5;
         if (h->seq_tokens < 1) h->seq_tokens = 1;
         /* the kernels' shared-memory limits are a per-device setting: set them for this handle's device */
         OPEN_CK(sp_graph_prepare(), "decode kernel attributes");

@@ -257,48 +257,32 @@ __global__ void __launch_bounds__(256) k_b_router(SpDims d, SpLayerDev L, BView 
         }
 }
 
-/* The same logits for a handful of tokens: one block per expert, so that NE blocks share the router
- * matrix between them instead of NE/16 (a batch this small is bound by the latency of one block's
- * loop, not by arithmetic). The expert's row is staged in shared memory; warp w takes tokens w, w+8, ...
- * four at a time, every (expert, token) chain in the order given above. */
+/* The same logits for a handful of tokens: one block per (expert, eight tokens), so that a small batch
+ * still spreads over the machine (it is bound by the latency of one block's loop, not by arithmetic).
+ * The expert's row is staged in shared memory; warp w takes token 8*blockIdx.y + w, lane l the float4
+ * groups l, l+32, ... in the order given above. */
 __global__ void __launch_bounds__(256) k_b_router_small(SpDims d, SpLayerDev L, BView v, int M) {
     extern __shared__ __align__(16) float4 rw[];               /* [E/4] */
     const int E = d.E, G = E >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, e = blockIdx.x;
     const float4 *wrow = reinterpret_cast<const float4 *>(L.router_w + (size_t)e * E);
     for (int g = threadIdx.x; g < G; g += 256) rw[g] = __ldg(wrow + g);
     __syncthreads();
-    const float bias = L.router_bias ? __ldg(L.router_bias + e) : 0.0f;
-    for (int t0 = warp; t0 < M; t0 += 32) {
-        const float4 *x[4]; float acc[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int t = t0 + 8 * j;
-            x[j] = reinterpret_cast<const float4 *>(v.rin + (size_t)(t < M ? t : t0) * E);
-            acc[j] = 0.0f;
-        }
-#pragma unroll 4
-        for (int g = lane; g < G; g += 32) {
-            const float4 w = rw[g];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float4 xv = x[j][g];
-                float a = acc[j];
-                a = __fmaf_rn(w.x, xv.x, a); a = __fmaf_rn(w.y, xv.y, a);
-                a = __fmaf_rn(w.z, xv.z, a); a = __fmaf_rn(w.w, xv.w, a);
-                acc[j] = a;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float r = warp_tree(acc[j]);
-            const int t = t0 + 8 * j;
-            if (lane == 0 && t < M) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, bias) : r;
-        }
+    const int t = blockIdx.y * 8 + warp;
+    if (t >= M) return;
+    const float4 *x = reinterpret_cast<const float4 *>(v.rin + (size_t)t * E);
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int g = lane; g < G; g += 32) {
+        const float4 w = rw[g], xv = x[g];
+        acc = __fmaf_rn(w.x, xv.x, acc); acc = __fmaf_rn(w.y, xv.y, acc);
+        acc = __fmaf_rn(w.z, xv.z, acc); acc = __fmaf_rn(w.w, xv.w, acc);
     }
+    const float r = warp_tree(acc);
+    if (lane == 0) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, __ldg(L.router_bias + e)) : r;
 }
 constexpr int kRouterSmallM = 64;
 void launch_router(const SpDims &d, const SpLayerDev &L, BView &v, int M, cudaStream_t st, int *nl) {
-    if (M <= kRouterSmallM && (size_t)d.E * 4 <= 48 * 1024) k_b_router_small<<<d.NE, 256, (size_t)d.E * 4, st>>>(d, L, v, M);
+    if (M <= kRouterSmallM && (size_t)d.E * 4 <= 48 * 1024) k_b_router_small<<<dim3((unsigned)d.NE, (unsigned)((M + 7) / 8)), 256, (size_t)d.E * 4, st>>>(d, L, v, M);
     else k_b_router<<<dim3((d.NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M);
     (*nl)++;
 }

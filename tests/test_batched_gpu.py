@@ -26,6 +26,26 @@ def test_batched_decode_flavour_small(cfg, n_layers, M):
     eng.close()
 
 
+@pytest.mark.parametrize("cfg,n_layers,M", [(orc.TINY, 2, 2), (orc.SMALL, 2, 5), (orc.GEMMA, 1, 3)])
+def test_small_decode_batch_both_routes(cfg, n_layers, M, monkeypatch):
+    """A decode batch of a few tokens runs token by token through the single-token graph by default;
+    SP_MOE_SEQ_TOKENS=1 sends it to the batched kernels instead (tensor-core row dots, per-expert router
+    blocks). Both give the checker's result and each other's, bit for bit, routing tables included."""
+    x = np.random.default_rng(50 + M).standard_normal((M, cfg["E"])).astype(np.float32)
+    outs = []
+    for seq in ("8", "1"):
+        monkeypatch.setenv("SP_MOE_SEQ_TOKENS", seq)
+        eng, host = make_stack(cfg, n_layers, seed=23, rand_norms=True, max_tokens=M)
+        outs.append(eng.forward(x, flavour=A))
+        eng.close()
+    ry, rsel, rwts, margin = oracle_stack(cfg, host, x, A)
+    for y, sel, wts in outs:
+        assert np.array_equal(sel, rsel), f"expert ids differ (min margin {margin:.3e})"
+        assert_close(y, ry, "small decode batch")
+    assert np.array_equal(outs[0][0].view(np.uint32), outs[1][0].view(np.uint32))
+    assert np.array_equal(outs[0][2].view(np.uint32), outs[1][2].view(np.uint32))
+
+
 @pytest.mark.parametrize("cfg,n_layers,M", [(orc.TINY, 2, 3), (orc.SMALL, 2, 40), (orc.SMALL, 1, 1)])
 def test_batched_prefill_flavour_small(cfg, n_layers, M):
     eng, host = make_stack(cfg, n_layers, seed=22, rand_norms=True, max_tokens=M)
