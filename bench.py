@@ -302,7 +302,58 @@ def small_batch_leg(eng, NL, local_rank, rank, peak_gbs):
         eng.status()
         out[f"M={M}"] = {"tokens_per_s": M / (ms / 1e3), "ms_per_step": ms, "distinct_experts_per_layer_mean": sum(U) / len(U),
                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak_gbs, "unit": "GB/s", "frac": gbs / peak_gbs, "algorithmic_bytes": nbytes},
+                         "route": "token by token through the single-token graph" if M <= int(os.environ.get("SP_MOE_SEQ_TOKENS", "5")) else "batched kernels (mma.sync row dots)",
                          "row0_equals_single_token_step": bool(torch.equal(y1.view(torch.int32), y[0].view(torch.int32)))}
+    return out
+
+
+# ---------------------------------------------------------------- prefill with fewer MMA terms per k-step
+def prefill_terms_leg(NL, PT, local_rank):
+    """The same prefill pass with the weight rounded to fp16 (2 MMAs per k-step) and with the activation
+    rounded too (1 MMA: the reference's SP_G4_GEMM_F16 mode), beside the exact 3-term default. The error is
+    taken over ONE layer against the 3-term result (deeper stacks diverge through top-k flips of near-tied
+    experts, which says nothing about the arithmetic)."""
+    import torch
+    from kairos_engine_b200 import FLAVOUR_PREFILL, MoeEngine, synth
+    dev = f"cuda:{local_rank}"
+    x = synth.make_inputs(CFG, PT, seed=90, device=dev)
+    out, ref1 = {}, None
+    for terms in (3, 2, 1):
+        os.environ["SP_MOE_PREFILL_TERMS"] = str(terms)
+        try:
+            eng = MoeEngine(n_layers=NL, max_tokens=PT, device=local_rank, **CFG)
+        finally:
+            del os.environ["SP_MOE_PREFILL_TERMS"]
+        for L in range(NL):
+            layer = synth.make_layer(CFG, 1000 * L, device=dev)
+            eng.upload_layer(L, layer, on_device=True)
+            del layer
+        y = torch.empty_like(x)
+        y1 = torch.empty_like(x)
+        eng.forward_dev(x, y1, 0, 1, FLAVOUR_PREFILL)
+        for _ in range(2):
+            eng.forward_dev(x, y, 0, NL, FLAVOUR_PREFILL)
+        eng.status()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            eng.forward_dev(x, y, 0, NL, FLAVOUR_PREFILL)
+        e1.record()
+        torch.cuda.synchronize()
+        eng.status()
+        ms = e0.elapsed_time(e1) / 3
+        rec = {"tokens_per_s": PT / (ms / 1e3), "ms_per_pass": ms}
+        if ref1 is None:
+            ref1 = y1.double()
+        else:
+            d = y1.double() - ref1
+            rec["one_layer_rel_l2_vs_3_terms"] = float(d.norm() / ref1.norm())
+            rec["one_layer_max_abs_vs_3_terms"] = float(d.abs().max())
+        out[f"terms={terms}"] = rec
+        eng.close()
+        del eng, y, y1
+        torch.cuda.empty_cache()
+    out["switch"] = "SP_MOE_PREFILL_TERMS (read when a handle opens); 3 is the default and the headline"
     return out
 
 
@@ -550,6 +601,7 @@ def run_ours(args, rank, local_rank, world):
             eng.set_router_bias(L, bias)
     small = extra(small_batch_leg, eng, NL, local_rank, rank, peak) if (PT and world == 1) else None
     igemm = extra(int_gemm_leg, local_rank) if (PT and world == 1) else None
+    terms = extra(prefill_terms_leg, NL, PT, local_rank) if (PT and world == 1) else None
 
     if rank == 0:
         bytes_per_launch = NL * synth.algorithmic_bytes_per_layer(CFG, M=1, U=CFG["NU"])
@@ -577,6 +629,8 @@ def run_ours(args, rank, local_rank, world):
             line["small_batch"] = small
         if igemm:
             line["int_gemm"] = igemm
+        if terms:
+            line["prefill_terms"] = terms
         if world == 1 and not args.no_cpu:
             try:
                 line["cpu_baseline"], line["parity"]["decode_vs_checker"] = cpu_baseline_leg(eng, torch)

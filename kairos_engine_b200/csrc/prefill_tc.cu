@@ -63,7 +63,8 @@ struct TcArgs {
 
 __device__ __forceinline__ int kpos(int e) { return ((e & 3) << 1) | (e >> 2); }     /* slot of element e inside its group of 8 */
 
-/* one Q4B block (32 weights, one f16 scale) -> four 16-byte chunks of hi and of lo halves */
+/* one Q4B block (32 weights, one f16 scale) -> four 16-byte chunks of hi and (LO) of lo halves */
+template <bool LO>
 __device__ __forceinline__ void unpack_block(const int4 &w, unsigned short scale, unsigned char *a_hi, unsigned char *a_lo,
                                              uint32_t rowoff, int r7, int g0) {
     const __half2 s2 = __half2half2(__ushort_as_half(scale));
@@ -78,17 +79,18 @@ __device__ __forceinline__ void unpack_block(const int4 &w, unsigned short scale
             const uint32_t bits = ((t >> (4 * j)) & 0x000F000Fu) | 0x64006400u;        /* halves 1024 + (code + 8): elements j, j + 4 */
             const __half2 c = __hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032);
             const __half2 h = __hmul2(c, s2);
-            const __half2 l = __hfma2(c, s2, __hneg2(h));
             hi[j] = *reinterpret_cast<const uint32_t *>(&h);
-            lo[j] = *reinterpret_cast<const uint32_t *>(&l);
+            if (LO) { const __half2 l = __hfma2(c, s2, __hneg2(h)); lo[j] = *reinterpret_cast<const uint32_t *>(&l); }
         }
         const uint32_t off = rowoff + (uint32_t)(((g0 + q) ^ r7) << 4);
         *reinterpret_cast<uint4 *>(a_hi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4 *>(a_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        if (LO) *reinterpret_cast<uint4 *>(a_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
 }
 
-template <bool PAIR>
+/* TERMS: 3 = all of w_hi*x_hi + w_lo*x_hi + w_hi*x_lo (exact to 2^-22); 2 = the weight rounded to fp16
+ * (w_hi*x_hi + w_hi*x_lo); 1 = fp16 x fp16, the reference's SP_G4_GEMM_F16 mode (CF:13350-13365). */
+template <bool PAIR, int TERMS>
 __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const __grid_constant__ TcMaps maps) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -132,10 +134,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
                 for (int kb = 0; kb < KB; kb++, it++) {
                     const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
                     if (!mbar_wait(empty(s), ph ^ 1, abort_flag)) { failed = true; break; }
-                    mbar_expect_tx(full(s), 2 * kBHalf);
+                    mbar_expect_tx(full(s), TERMS >= 2 ? 2 * kBHalf : kBHalf);
                     const uint32_t dst = sbase + s * kStageBytes + 2 * kAHalf;
                     tma_load_2d(dst, &maps.hi, kb * kBK, row0, full(s));
-                    tma_load_2d(dst + kBHalf, &maps.lo, kb * kBK, row0, full(s));
+                    if (TERMS >= 2) tma_load_2d(dst + kBHalf, &maps.lo, kb * kBK, row0, full(s));
                 }
             }
             if (failed || *abort_flag) __nanosleep(100000);          /* let copies in flight land before the CTA leaves */
@@ -162,8 +164,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
                         const uint64_t whi = make_desc(st + ks * 32), wlo = make_desc(st + kAHalf + ks * 32);
                         const uint64_t xhi = make_desc(st + 2 * kAHalf + ks * 32), xlo = make_desc(st + 2 * kAHalf + kBHalf + ks * 32);
                         umma_f16(d0, xhi, whi, idesc, (kb | ks) ? 1u : 0u);
-                        umma_f16(d0, xhi, wlo, idesc, 1u);
-                        umma_f16(d0, xlo, whi, idesc, 1u);
+                        if (TERMS >= 3) umma_f16(d0, xhi, wlo, idesc, 1u);
+                        if (TERMS >= 2) umma_f16(d0, xlo, whi, idesc, 1u);
                     }
                     umma_commit(empty(s));                          /* stage reusable once these MMAs have read it */
                 }
@@ -194,8 +196,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_tc_gemm(const TcArgs a, const _
                 const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
                 if (!mbar_wait(empty(s), ph ^ 1, abort_flag)) { failed = true; break; }
                 unsigned char *ahi = smem + s * kStageBytes, *alo = ahi + kAHalf;
-                unpack_block(w0, (unsigned short)(s2 & 0xFFFFu), ahi, alo, rowoff, r7, 0);
-                unpack_block(w1, (unsigned short)(s2 >> 16), ahi, alo, rowoff, r7, 4);
+                unpack_block<TERMS >= 3>(w0, (unsigned short)(s2 & 0xFFFFu), ahi, alo, rowoff, r7, 0);
+                unpack_block<TERMS >= 3>(w1, (unsigned short)(s2 >> 16), ahi, alo, rowoff, r7, 4);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full(s));
@@ -344,6 +346,7 @@ struct SpTcPlan {
     __half *nx_hi, *nx_lo, *hd_hi, *hd_lo, *in_hi, *in_lo, *h_hi, *h_lo;
     int *tiles_sh, *ntiles_sh, *tiles_r, *ntiles_r, *offsets, *gather, *rowmap;
     int cap_sh, cap_r;
+    int terms;                                         /* MMAs per k-step: 3, 2 or 1 */
     TcMaps m_nx, m_hd, m_in, m_h;
 };
 
@@ -394,8 +397,17 @@ cudaError_t sp_tc_create(const SpDims &d, int max_tokens, int max_rows, SpTcPlan
     mk(&p->m_hd.hi, p->hd_hi, d.FFS, p->Mcap); mk(&p->m_hd.lo, p->hd_lo, d.FFS, p->Mcap);
     mk(&p->m_in.hi, p->in_hi, d.E, p->Rcap); mk(&p->m_in.lo, p->in_lo, d.E, p->Rcap);
     mk(&p->m_h.hi, p->h_hi, d.FFE, p->Rcap); mk(&p->m_h.lo, p->h_lo, d.FFE, p->Rcap);
-    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (m == cudaSuccess) m = cudaFuncSetAttribute(k_tc_gemm<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    /* house convention: behaviour switches are SP_* variables read once. 3 (default) keeps every product the fp32
+     * reference arithmetic sees down to 2^-22; 2 rounds the dequantised weight to fp16; 1 also rounds the activation. */
+    const char *tv = getenv("SP_MOE_PREFILL_TERMS");
+    p->terms = tv ? atoi(tv) : 3;
+    if (p->terms < 1 || p->terms > 3) p->terms = 3;
     if (m != cudaSuccess) { cudaFree(p->base); delete p; return m; }
     *out = p; *bytes = o;
     return cudaSuccess;
@@ -405,7 +417,10 @@ void sp_tc_destroy(SpTcPlan *p) { if (!p) return; if (p->base) cudaFree(p->base)
 namespace {
 template <bool PAIR>
 void launch_gemm(const SpTcPlan *p, const TcArgs &a, const TcMaps &maps, cudaStream_t st, int *nl) {
-    k_tc_gemm<PAIR><<<p->sms, kThreads, kSmemBytes, st>>>(a, maps); (*nl)++;
+    if (p->terms == 3) k_tc_gemm<PAIR, 3><<<p->sms, kThreads, kSmemBytes, st>>>(a, maps);
+    else if (p->terms == 2) k_tc_gemm<PAIR, 2><<<p->sms, kThreads, kSmemBytes, st>>>(a, maps);
+    else k_tc_gemm<PAIR, 1><<<p->sms, kThreads, kSmemBytes, st>>>(a, maps);
+    (*nl)++;
 }
 }  // namespace
 

@@ -55,6 +55,30 @@ def test_gemma_geometry(M):
     eng.close()
 
 
+@pytest.mark.parametrize("terms", [2, 1])
+def test_fewer_terms_one_layer(terms, monkeypatch):
+    """SP_MOE_PREFILL_TERMS=2 rounds the dequantised weight to fp16, =1 rounds the activation as well (the
+    reference's SP_G4_GEMM_F16 mode). One Gemma-geometry layer stays inside the gate; the measured error is
+    reported so the cost of each dropped term is on record. Expert ids do not depend on the GEMMs."""
+    cfg = orc.GEMMA
+    M = 32
+    monkeypatch.setenv("SP_MOE_PREFILL_TERMS", str(terms))
+    eng, host = make_stack(cfg, 1, seed=6, max_tokens=M)
+    x = np.random.default_rng(77).standard_normal((M, cfg["E"])).astype(np.float32)
+    y, sel, wts = eng.forward(x, flavour=B)
+    ry, rsel, rwts, margin = oracle_stack(cfg, host, x, B)
+    assert np.array_equal(sel, rsel)
+    d = y.astype(np.float64) - ry.astype(np.float64)
+    max_abs, rel = np.abs(d).max(), np.linalg.norm(d) / np.linalg.norm(ry.astype(np.float64))
+    print(f"terms={terms}: max-abs {max_abs:.3e} rel-L2 {rel:.3e}")
+    if terms == 2:
+        assert_close(y, ry, "tensor-core prefill, weight rounded to fp16")           # inside the gate
+    else:
+        # fp16 x fp16 leaves the gate on max-abs (about 2.4e-3 against 2e-3 here): an opt-in mode, never the default
+        assert rel <= 1e-3 and max_abs <= 5e-3
+    eng.close()
+
+
 def test_skewed_routing_many_rows_on_one_expert():
     from kairos_engine_b200 import synth
     cfg = orc.SMALL
