@@ -203,55 +203,69 @@ __global__ void __launch_bounds__(256) k_b_prep(SpDims d, SpLayerDev L, const fl
 /* ---------------------------------------------------------------- K2: router logits, fp32, fixed order
  * lane l takes the float4 groups q = l, l+32, ... with acc = fma(w, x, acc) over the four
  * elements in order, then the shuffle tree (the same order the decode kernel uses). One block =
- * 16 experts x 16 tokens; E is walked in chunks of 64 float4 groups staged in shared memory, and
- * each warp keeps a 4-expert x 8-token register tile, so every (expert, token) chain keeps the
- * order above while 32 independent chains hide the FMA latency. */
-constexpr int kRouterTE = 16, kRouterTT = 16;
-__global__ void __launch_bounds__(256) k_b_router(SpDims d, SpLayerDev L, BView v, int M) {
-    __shared__ float4 wS[kRouterTE][64];
-    __shared__ float4 xS[kRouterTT][64];
+ * 32 experts x 16 tokens; E is walked in chunks of 32 float4 groups staged in shared memory, and
+ * each warp keeps an 8-expert x 8-token register tile (16 shared-memory loads per 256 FMAs), so every
+ * (expert, token) chain keeps the order above while 64 independent chains hide the FMA latency. */
+constexpr int kRouterTE = 32, kRouterTT = 16;
+constexpr size_t kRouterSmem = 2 * (size_t)(kRouterTE + kRouterTT) * 32 * sizeof(float4);     /* two stages of 24 KB */
+/* 16-byte asynchronous copy that writes zeros when `take` is false (the source address stays valid either way) */
+__device__ __forceinline__ void cp_async16_zfill(void *smem_dst, const void *src, bool take) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"((unsigned)__cvta_generic_to_shared(smem_dst)), "l"(src), "r"(take ? 16 : 0) : "memory");
+}
+__global__ void __launch_bounds__(256, 2) k_b_router(SpDims d, SpLayerDev L, BView v, int M) {
+    extern __shared__ __align__(16) float4 rsm[];              /* [2] x { w[32][32], x[16][32] }: the next chunk lands while this one is used */
     const int E = d.E, G = E >> 2, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int we = warp & 3, wt = warp >> 2;
     const int e0 = blockIdx.x * kRouterTE, t0 = blockIdx.y * kRouterTT;
-    float acc[4][8];
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
-    const float4 zero = make_float4(0, 0, 0, 0);
-    for (int c0 = 0; c0 < G; c0 += 64) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 16 * 64; idx += 256) {
-            const int row = idx >> 6, g = idx & 63, gg = c0 + g;
-            wS[row][g] = (gg < G && e0 + row < d.NE) ? __ldg(reinterpret_cast<const float4 *>(L.router_w + (size_t)(e0 + row) * E) + gg) : zero;
-            xS[row][g] = (gg < G && t0 + row < M) ? *(reinterpret_cast<const float4 *>(v.rin + (size_t)(t0 + row) * E) + gg) : zero;
+    auto stage = [&](int c0, int buf) {                         /* warp w stages expert rows w, w+8, w+16, w+24 and token rows w, w+8 */
+        float4 *wS = rsm + (size_t)buf * (kRouterTE + kRouterTT) * 32, *xS = wS + kRouterTE * 32;
+        const int gg = c0 + lane; const bool gok = gg < G; const int gc = gok ? gg : 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int row = warp + 8 * k; const bool ok = gok && e0 + row < d.NE;
+            cp_async16_zfill(wS + row * 32 + lane, reinterpret_cast<const float4 *>(L.router_w + (size_t)(ok ? e0 + row : 0) * E) + gc, ok);
         }
-        __syncthreads();
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int g = lane + 32 * h;            /* zero padding beyond E leaves acc unchanged: fma(0, 0, acc) = acc */
-            float4 w[4], x[8];
-#pragma unroll
-            for (int i = 0; i < 4; i++) w[i] = wS[4 * we + i][g];
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = xS[8 * wt + j][g];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float a = acc[i][j];
-                    a = __fmaf_rn(w[i].x, x[j].x, a); a = __fmaf_rn(w[i].y, x[j].y, a);
-                    a = __fmaf_rn(w[i].z, x[j].z, a); a = __fmaf_rn(w[i].w, x[j].w, a);
-                    acc[i][j] = a;
-                }
+        for (int k = 0; k < 2; k++) {
+            const int row = warp + 8 * k; const bool ok = gok && t0 + row < M;
+            cp_async16_zfill(xS + row * 32 + lane, reinterpret_cast<const float4 *>(v.rin + (size_t)(ok ? t0 + row : 0) * E) + gc, ok);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nch = (G + 31) >> 5;
+    stage(0, 0);
+    for (int c = 0; c < nch; c++) {
+        if (c + 1 < nch) { stage(32 * (c + 1), (c + 1) & 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float4 *wS = rsm + (size_t)(c & 1) * (kRouterTE + kRouterTT) * 32, *xS = wS + kRouterTE * 32;
+        float4 w[8];                                            /* zero padding beyond E leaves acc unchanged: fma(0, 0, acc) = acc */
+#pragma unroll
+        for (int i = 0; i < 8; i++) w[i] = wS[(8 * we + i) * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 x = xS[(8 * wt + j) * 32 + lane];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float a = acc[i][j];
+                a = __fmaf_rn(w[i].x, x.x, a); a = __fmaf_rn(w[i].y, x.y, a);
+                a = __fmaf_rn(w[i].z, x.z, a); a = __fmaf_rn(w[i].w, x.w, a);
+                acc[i][j] = a;
+            }
+        }
+        __syncthreads();                                        /* this stage is overwritten two chunks on */
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const float r = warp_tree(acc[i][j]);
-            const int e = e0 + 4 * we + i, t = t0 + 8 * wt + j;
+            const int e = e0 + 8 * we + i, t = t0 + 8 * wt + j;
             if (lane == 0 && e < d.NE && t < M)
                 v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, __ldg(L.router_bias + e)) : r;
         }
@@ -283,7 +297,7 @@ __global__ void __launch_bounds__(256) k_b_router_small(SpDims d, SpLayerDev L, 
 constexpr int kRouterSmallM = 64;
 void launch_router(const SpDims &d, const SpLayerDev &L, BView &v, int M, cudaStream_t st, int *nl) {
     if (M <= kRouterSmallM && (size_t)d.E * 4 <= 48 * 1024) k_b_router_small<<<dim3((unsigned)d.NE, (unsigned)((M + 7) / 8)), 256, (size_t)d.E * 4, st>>>(d, L, v, M);
-    else k_b_router<<<dim3((d.NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, 0, st>>>(d, L, v, M);
+    else k_b_router<<<dim3((d.NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, kRouterSmem, st>>>(d, L, v, M);
     (*nl)++;
 }
 
@@ -759,14 +773,14 @@ void launch_rows(const GroupArgs &g, int groups, cudaStream_t st, int *nl) {
 __global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const float *x, BView v, const float *eo, const int *pair_index, float *y) {
     extern __shared__ __align__(16) float fsm[];              /* [2][E] */
     __shared__ double sh[256];
-    const int t = blockIdx.x, E = d.E, NU = d.NU;
-    float *va = fsm, *vb = fsm + E;
+    const int t = blockIdx.x, E = d.E, NU = d.NU, tid = threadIdx.x;
     float cw[SP_MAX_NU]; size_t er[SP_MAX_NU];
 #pragma unroll
     for (int k = 0; k < SP_MAX_NU; k++) {
         cw[k] = k < NU ? v.cw[(size_t)t * NU + k] : 0.0f;
         er[k] = k < NU ? (size_t)(pair_index ? pair_index[(size_t)t * NU + k] : t * NU + k) * E : 0;
     }
+    float *va = fsm, *vb = fsm + E;
 #pragma unroll 4
     for (int i = threadIdx.x; i < E; i += 256) {
         float acc = 0.0f;
@@ -789,6 +803,8 @@ __global__ void __launch_bounds__(256) k_b_finish(SpDims d, SpLayerDev L, const 
         y[(size_t)t * E + i] = __fadd_rn(x[(size_t)t * E + i], __fmul_rn(__fmul_rn(va[i], sc3), __ldg(L.post_ffw + i)));
 }
 
+static size_t finish_smem(int E) { return (size_t)2 * E * 4; }
+
 template <bool FA>
 cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *x, float *y, int32_t *sel, float *wts,
                       BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
@@ -804,7 +820,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
         if (e != cudaSuccess) return e;
         e = sp_tc_routed(tc, d, L, M * NU, v.in_f, gather, off, rowmap, v.eo, status, st, nl);
         if (e != cudaSuccess) return e;
-        k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
+        k_b_finish<<<M, 256, finish_smem(E), st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
         return cudaGetLastError();
     }
     GroupArgs g{};
@@ -829,7 +845,7 @@ cudaError_t run_layer(const SpDims &d, const SpLayerDev &L, int M, const float *
     g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E; g.count = v.count; g.list = v.list; g.list_stride = M;
     g.in = FFE; g.rows = E; g.act_div = 1; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = v.eo; g.out_stride = E;
     launch_rows<FA, false>(g, NE, st, nl);
-    k_b_finish<<<M, 256, (size_t)2 * E * 4, st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
+    k_b_finish<<<M, 256, finish_smem(E), st>>>(d, L, x, v, v.eo, nullptr, y); (*nl)++;
     return cudaGetLastError();
 }
 
@@ -1013,7 +1029,7 @@ cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, co
     *nlaunch = 0;
     if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices) return cudaErrorInvalidValue;
     BView v = bview_slice(d, s, t0, slice);
-    k_b_finish<<<M, 256, (size_t)2 * d.E * 4, st>>>(d, L, x, v, pair_rows, pair_index, y); (*nlaunch)++;
+    k_b_finish<<<M, 256, finish_smem(d.E), st>>>(d, L, x, v, pair_rows, pair_index, y); (*nlaunch)++;
     return cudaGetLastError();
 }
 
