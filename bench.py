@@ -37,11 +37,11 @@ CFG = dict(E=2816, NE=128, NU=8, FFE=704, FFS=2112, eps=1e-6)
 N_LAYERS = 30
 TOKENS_PER_STEP = 256
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers): taken with
-#   ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none --cache-control none -k regex:k_ds_ ...
-# on a 2-layer stack (python bench.py --steps 1 --warmup 3 --tokens-per-step 1 --layers 2 --no-cpu --no-prefill),
-# per layer, times 30 (the traffic is the same for every layer); None until a capture of the current kernels exists
-NCU_TRAFFIC_BYTES_PER_LAYER = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers), per layer: taken with
+#   ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --clock-control none --cache-control none
+#       -k regex:'k_ds_|k_dg_' -s 1092 -c 364 python bench.py --steps 1 --warmup 3 --tokens-per-step 4 --no-cpu --no-prefill
+# (4 tokens x 30 layers, caches kept between kernels): 1,176,572,800 B per token against 1,149,957,120 algorithmic.
+NCU_TRAFFIC_BYTES_PER_LAYER = 39219093
 
 
 def measured_peaks():
