@@ -37,11 +37,12 @@ CFG = dict(E=2816, NE=128, NU=8, FFE=704, FFS=2112, eps=1e-6)
 N_LAYERS = 30
 TOKENS_PER_STEP = 256
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode graph launch (one token, 30 layers), per layer: taken with
-#   ncu --metrics gpu__time_duration.sum,dram__bytes_read.sum,dram__bytes_write.sum --clock-control none --cache-control none
-#       -k regex:'k_ds_|k_dg_' -s 1092 -c 364 python bench.py --steps 1 --warmup 3 --tokens-per-step 4 --no-cpu --no-prefill
-# (4 tokens x 30 layers, caches kept between kernels): 1,176,572,800 B per token against 1,149,957,120 algorithmic.
-NCU_TRAFFIC_BYTES_PER_LAYER = 39219093
+# dram__bytes_read.sum + dram__bytes_write.sum of the three decode kernels of one layer, from one ncu capture of a
+# 2-layer stack (six launches = one token; L2 flushed before each kernel, prefetch hints off):
+#   SP_MOE_STAGED_FLAGS=0 ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:k_ds_ -s 18 -c 6
+#       python bench.py --steps 1 --warmup 3 --tokens-per-step 1 --layers 2 --no-cpu --no-prefill
+# 38,507,392 B per layer against 38,331,904 algorithmic; the traffic is the same for every layer, so a launch is 30x that.
+NCU_TRAFFIC_BYTES_PER_LAYER = 38507392
 
 
 def measured_peaks():

@@ -294,7 +294,10 @@ __global__ void __launch_bounds__(256) k_b_router_small(SpDims d, SpLayerDev L, 
     const float r = warp_tree(acc);
     if (lane == 0) v.logits[(size_t)t * d.NE + e] = L.router_bias ? __fadd_rn(r, __ldg(L.router_bias + e)) : r;
 }
-constexpr int kRouterSmallM = 64;
+#ifndef SP_ROUTER_SMALL_M
+#define SP_ROUTER_SMALL_M 64
+#endif
+constexpr int kRouterSmallM = SP_ROUTER_SMALL_M;   /* up to this many tokens the per-(expert, eight tokens) blocks beat the tiled kernel */
 void launch_router(const SpDims &d, const SpLayerDev &L, BView &v, int M, cudaStream_t st, int *nl) {
     if (M <= kRouterSmallM && (size_t)d.E * 4 <= 48 * 1024) k_b_router_small<<<dim3((unsigned)d.NE, (unsigned)((M + 7) / 8)), 256, (size_t)d.E * 4, st>>>(d, L, v, M);
     else k_b_router<<<dim3((d.NE + kRouterTE - 1) / kRouterTE, (M + kRouterTT - 1) / kRouterTT), 256, kRouterSmem, st>>>(d, L, v, M);

@@ -165,6 +165,36 @@ int main(void) {
         cudaFree(sel_asc); cudaFree(counts); cudaFree(pair_index); cudaFree(cw); cudaFree(rows); cudaFree(rows_out); cudaFree(y_st); cudaFree(off_dev); cudaFree(roff); cudaFree(ridx);
     }
 
+    /* ---- the expert-parallel loop inside the library, as a world of one rank: its own NCCL communicator,
+     * every exchange a send to itself; both exchange kinds must reproduce sp_moe_forward_dev bit for bit.
+     * Where libnccl is absent the entries say so and the section is skipped. */
+    {
+        unsigned char id[128];
+        const int rc_id = sp_moe_ep_unique_id(id);
+        if (rc_id == SP_MOE_EUNSUPPORTED) printf("note: no NCCL library here, expert-parallel loop not exercised\n");
+        else {
+            void *comm = NULL;
+            CHECK(rc_id == SP_MOE_OK, "sp_moe_ep_unique_id");
+            CHECK(sp_moe_ep_comm_create(id, 1, 0, &comm) == SP_MOE_OK && comm != NULL, "sp_moe_ep_comm_create");
+            CHECK(sp_moe_ep_comm_create(id, 1, 3, &comm) == SP_MOE_EBADARG, "comm_create must refuse rank >= n_ranks");
+            const int M = MT;
+            float *y_ep = (float *)dev_copy(NULL, M * E * 4);
+            for (int flavour = 0; flavour < 2 && comm; flavour++)
+                for (int cap = 0; cap <= M * NU; cap += M * NU) {          /* exact exchange, then padded with room for every pair */
+                    CHECK(sp_moe_ep_forward_dev(h, comm, 1, 0, 0, NL, flavour, M, x_dev, y_ep, cap, 1, st) == SP_MOE_OK, "sp_moe_ep_forward_dev (flavour %d, capacity %d)", flavour, cap);
+                    CHECK(sp_moe_forward_dev(h, 0, NL, flavour, M, x_dev, y_dev, NULL, NULL, st) == SP_MOE_OK, "forward_dev");
+                    CHECK(sp_moe_status(h) == SP_MOE_OK, "status after the expert-parallel loop");
+                    CUDA_OK(cudaMemcpy(y, y_ep, M * E * 4, cudaMemcpyDeviceToHost)); CUDA_OK(cudaMemcpy(y2, y_dev, M * E * 4, cudaMemcpyDeviceToHost));
+                    CHECK(memcmp(y, y2, M * E * 4) == 0, "library loop on one rank == sp_moe_forward_dev, bit for bit (flavour %d, capacity %d)", flavour, cap);
+                    CHECK(sp_moe_ep_last_rows(h) == (cap ? cap : M * NU), "sp_moe_ep_last_rows = %lld", sp_moe_ep_last_rows(h));
+                }
+            CHECK(sp_moe_ep_forward_dev(h, comm, 3, 0, 0, NL, 0, M, x_dev, y_ep, 0, 1, st) == SP_MOE_EBADARG, "ep_forward must refuse n_ranks that does not divide NE");
+            CHECK(sp_moe_ep_forward_dev(h, NULL, 1, 0, 0, NL, 0, M, x_dev, y_ep, 0, 1, st) == SP_MOE_EBADARG, "ep_forward must refuse a NULL communicator");
+            if (comm) CHECK(sp_moe_ep_comm_destroy(comm) == SP_MOE_OK, "sp_moe_ep_comm_destroy");
+            cudaFree(y_ep);
+        }
+    }
+
     /* ---- the file loader and the bias setter: refusals (a real file is the Python tests' job) */
     CHECK(sp_moe_load_sp_model(h, "/nonexistent/model.sp-model", NULL) == SP_MOE_EBADARG && strstr(sp_last_error(), "cannot open") != NULL, "load_sp_model must refuse a missing file");
     CHECK(sp_moe_load_sp_model(h, NULL, NULL) == SP_MOE_EBADARG, "load_sp_model must refuse NULL");
