@@ -28,7 +28,8 @@ enum {
     SP_STAGED_PREFETCH_SD = 1,      /* K1 asks L2 for the shared-expert down rows K2 will stage */
     SP_STAGED_PREFETCH_DN = 2,      /* K2 asks L2 for the routed down rows K3 will stage */
     SP_STAGED_PREFETCH_NEXT = 4,    /* K3 asks L2 for the next layer's router rows and shared gate/up rows */
-    SP_STAGED_DEFAULT = 7
+    SP_STAGED_MMA_DN = 8,           /* K3 takes its row dots on mma.sync (16-row tiles) instead of dp4a chains; same bits */
+    SP_STAGED_DEFAULT = 15
 };
 /* true when one CTA's slice of every phase fits `smem_optin` bytes of shared memory on a grid of `sms` CTAs */
 bool sp_staged_fits(const SpDims &d, int sms, size_t smem_optin);

@@ -128,6 +128,7 @@ struct Ctl {
     int sel_asc[SP_MAX_NU]; float cw[SP_MAX_NU]; int sel_desc[SP_MAX_NU]; float p_desc[SP_MAX_NU];
     unsigned gs_off[2], us_off[2];          /* K2: where the two runs' gate / up scale rows start */
     unsigned sdelta[SP_MAX_NU];             /* K3: bytes before the first scale row of each slot's span */
+    alignas(16) int zero[4];                /* K3: the activation operand of an MMA column that is not the lane's */
 };
 
 struct Lay1 { unsigned ctl, red, va, vb, ri, q_nx, q_in, s_nx, s_in, c_nx, c_in, st_r, st_gc, st_uc, st_gs, st_us, total; };
@@ -549,7 +550,11 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_up(SArgs a) {
 #pragma unroll 1
     for (int i = t; i < NE; i += kT) dsc[i] = __ldg(L.dexps_scale + i);
     __syncthreads();
-    pdl_launch();
+    /* The dependent kernel reads the selection before its own wait (to start its weight copies early). It can
+     * be launched only once every CTA has signalled, so CTA 0 - the one that publishes the selection - signals
+     * after the write and a fence (one lane, right there: a CTA's first signal is the one that counts); the
+     * others signal here. */
+    if (b != 0) pdl_launch();
     pdl_wait();
     STAMP(1, 1);
     if (warp < kRW) {
@@ -631,16 +636,25 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_up(SArgs a) {
             __syncwarp();
             if (lane < NU) { ctl->sel_asc[slot] = e; ctl->cw[slot] = __fmul_rn(wnorm, dsc[e]); ctl->p_desc[lane] = wnorm; }
             __syncwarp();
+            if (b == 0) asm volatile("bar.arrive 3, 64;" ::: "memory");      /* hands the selection to warp 1, which publishes it (below) */
             if (nP > 0) {                                 /* the selection exists: start the first parts of the routed rows at once */
                 const int n1 = nP - n0;
                 const GuGeo gg{nP, n0, c0, ctl->sel_asc[slot0], n1 > 0 ? ctl->sel_asc[slot0 + 1] : ctl->sel_asc[slot0], 1 << LP, FFE, rbE, sbE};
                 gu_issue(sm, ly, ctl, L, gg, 0, nparts < kGuAhead ? nparts : kGuAhead, lane);
             }
-            if (b == 0 && lane < NU) {
+        } else if (warp == 1 && b == 0) {
+            /* CTA 0 publishes the selection for the next kernel. A warp with nothing else to do takes it, so that the
+             * fence does not sit between the warp that feeds the copy engine and its copies; the CTA's signal to the
+             * dependent kernel follows every lane's fence. */
+            asm volatile("bar.sync 3, 64;" ::: "memory");
+            if (lane < NU) {
                 a.s.sel_asc[lane] = ctl->sel_asc[lane]; a.s.cw[lane] = ctl->cw[lane];
                 if (a.sel_out) a.sel_out[lane] = ctl->sel_desc[lane];
                 if (a.wts_out) a.wts_out[lane] = ctl->p_desc[lane];
+                __threadfence();
             }
+            __syncwarp();
+            if (lane == 0) pdl_launch();
         }
     } else {
         /* ---- the routed experts' input (for the pairs below), the shared expert's hidden vector, its down rows */
@@ -778,6 +792,86 @@ __device__ __forceinline__ void down_round(const unsigned char *sm, const Lay3 &
     }
 }
 
+/* ---- the same row dots on the tensor cores: one warp, 16 rows of one slot (rows ti*16 .. ti*16+15 of the CTA's
+ * slice), the row's 32-weight chunks four at a time. mma.sync m16n8k32 s8 x s8: the code nibbles moved to the top of
+ * a byte are 16 x code; the activation operand of MMA i is non-zero only in the column (chunk, 16-block) its k-slots
+ * belong to, so four MMAs leave, in lane (g, q), the two block sums of chunk 4j+q for rows g and g+8. That lane then
+ * does what lane (4j+q) % 32 does in row_dot - one accumulator per slot, chunks in ascending order, the same two fmas
+ * and one mul - and the slots are added in the shuffle tree's pairing. Rows past the slice repeat its last row and
+ * are dropped. Valid while a row has at most 24 chunks (six groups of four). */
+__device__ __forceinline__ void mma_s8_acc(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8_first(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1, int c) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+__device__ __forceinline__ float magic16_to_float(int c) { return __fmaf_rn(__int_as_float(c), 0.0625f, -786432.0f); }   /* bits 0x4B400000 + 16 S -> float(S) */
+constexpr int kMmaGroups = 6;
+
+__device__ __forceinline__ void down_tile_mma(const unsigned char *sm, const Lay3 &ly, Ctl *ctl, int *status, int s, int ti, int nj, int njm, int SGs,
+                                              unsigned rb, unsigned sb, int n32, int blk16, int lane, float *out) {
+    bar_wait(smem_u32(&ctl->bar[s / SGs]), &ctl->abort, status);
+    const int gq = lane >> 2, q = lane & 3;
+    const int r0 = ti * 16 + gq, r1 = r0 + 8;
+    const int rc0 = r0 < nj ? r0 : nj - 1, rc1 = r1 < nj ? r1 : nj - 1;
+    const unsigned char *c0 = sm + ly.st_c + ((unsigned)s * (unsigned)njm + (unsigned)rc0) * rb;
+    const unsigned char *c1 = sm + ly.st_c + ((unsigned)s * (unsigned)njm + (unsigned)rc1) * rb;
+    const unsigned char *sbase = sm + ly.st_s + (unsigned)s * ly.span_max + ctl->sdelta[s];
+    const unsigned char *sc0 = sbase + (unsigned)rc0 * sb, *sc1 = sbase + (unsigned)rc1 * sb;
+    const unsigned char *qh = sm + ly.q_h + (unsigned)s * (unsigned)blk16 * 16u;
+    const float *sxp = reinterpret_cast<const float *>(sm + ly.s_h) + (unsigned)s * (unsigned)blk16;
+    const unsigned char *zero = reinterpret_cast<const unsigned char *>(ctl->zero);
+    const bool bvalid = (gq >> 1) == q; const int bh = gq & 1;
+    float acc[8][2];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i][0] = acc[i][1] = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < kMmaGroups; jj++) {
+        if (4 * jj < n32) {                               /* warp-uniform */
+            const int c = 4 * jj + q; const bool cv = c < n32; const int cc = cv ? c : n32 - 1;
+            uint4 w0 = *reinterpret_cast<const uint4 *>(c0 + 16 * cc), w1 = *reinterpret_cast<const uint4 *>(c1 + 16 * cc);
+            if (!cv) { w0 = make_uint4(0, 0, 0, 0); w1 = w0; }
+            const float s0 = h2f(*reinterpret_cast<const unsigned short *>(sc0 + 2 * cc)), s1 = h2f(*reinterpret_cast<const unsigned short *>(sc1 + 2 * cc));
+            const unsigned x0[4] = {w0.x, w0.y, w0.z, w0.w}, x1[4] = {w1.x, w1.y, w1.z, w1.w};
+            unsigned a[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                a[i][0] = (x0[i] << 4) & 0xF0F0F0F0u; a[i][1] = (x1[i] << 4) & 0xF0F0F0F0u;
+                a[i][2] = x0[i] & 0xF0F0F0F0u;        a[i][3] = x1[i] & 0xF0F0F0F0u;
+            }
+            const uint4 l0 = *reinterpret_cast<const uint4 *>(bvalid && cv && bh == 0 ? qh + c * 32 : zero);
+            const uint4 l1 = *reinterpret_cast<const uint4 *>(bvalid && cv && bh == 1 ? qh + c * 32 + 16 : zero);
+            int ca[4], cb[4];
+            mma_s8_first(ca, a[0][0], a[0][1], a[0][2], a[0][3], l0.x, l0.y, kMagicBits);
+            mma_s8_first(cb, a[2][0], a[2][1], a[2][2], a[2][3], l1.x, l1.y, kMagicBits);
+            mma_s8_acc(ca, a[1][0], a[1][1], a[1][2], a[1][3], l0.z, l0.w);
+            mma_s8_acc(cb, a[3][0], a[3][1], a[3][2], a[3][3], l1.z, l1.w);
+            if (cv) {
+                const float2 s2 = *reinterpret_cast<const float2 *>(sxp + 2 * c);
+                acc[jj][0] = __fmaf_rn(s0, __fmaf_rn(magic16_to_float(ca[0]), s2.x, __fmul_rn(magic16_to_float(cb[1]), s2.y)), acc[jj][0]);
+                acc[jj][1] = __fmaf_rn(s1, __fmaf_rn(magic16_to_float(ca[2]), s2.x, __fmul_rn(magic16_to_float(cb[3]), s2.y)), acc[jj][1]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = acc[i][r];
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < o; i++) v[i] += v[i + o];         /* slots s+16, s+8, s+4 of the tree sit in this lane */
+        float k = v[0];
+        k += __shfl_down_sync(0xffffffffu, k, 2);
+        k += __shfl_down_sync(0xffffffffu, k, 1);
+        const int row = r ? r1 : r0;
+        if (q == 0 && row < nj) out[s * njm + row] = k;
+    }
+}
+
 template <int NIT>
 __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
     extern __shared__ __align__(128) unsigned char sm[];
@@ -800,19 +894,13 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
 #pragma unroll 1
         for (int i = 0; i < kDnBars; i++) mbar_init(smem_u32(&ctl->bar[i]), 1);
         ctl->abort = 0;
+        ctl->zero[0] = ctl->zero[1] = ctl->zero[2] = ctl->zero[3] = 0;
         fence_barrier_init();
     }
     __syncthreads();
     pdl_launch();
-    pdl_wait();
-    STAMP(2, 1);
-    /* this thread's first block of the experts' hidden vectors: requested before anything waits on the selection */
-    float hv[16];
-    if (t < nblk) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) { const float4 f = __ldcg(reinterpret_cast<const float4 *>(a.s.h + 16 * t) + i); hv[4 * i] = f.x; hv[4 * i + 1] = f.y; hv[4 * i + 2] = f.z; hv[4 * i + 3] = f.w; }
-    }
-    if (warp == 0) {                                      /* the selection is in memory: start this CTA's rows of every selected expert */
+    if (warp == 0) {                                      /* the selection was published and fenced before this kernel could be launched: start this
+                                                             CTA's rows of every selected expert now, before waiting for the predecessor's hidden vectors */
         const int e = lane < NU ? __ldcg(a.s.sel_asc + lane) : 0;
         const float w = lane < NU ? __ldcg(a.s.cw + lane) : 0.0f;
         if (lane < NU) { ctl->sel_asc[lane] = e; ctl->cw[lane] = w; }
@@ -836,6 +924,13 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
         }
     }
     STAMP(2, 5);
+    pdl_wait();
+    STAMP(2, 1);
+    float hv[16];
+    if (t < nblk) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float4 f = __ldcg(reinterpret_cast<const float4 *>(a.s.h + 16 * t) + i); hv[4 * i] = f.x; hv[4 * i + 1] = f.y; hv[4 * i + 2] = f.z; hv[4 * i + 3] = f.w; }
+    }
     if (t < nblk) quant_block16_store(hv, reinterpret_cast<int4 *>(q_h) + t, s_h + t, c_h + t);
 #pragma unroll 1
     for (int bq = t + kT; bq < nblk; bq += kT) quant_from_global(a.s.h + 16 * bq, reinterpret_cast<int4 *>(q_h) + bq, s_h + bq, c_h + bq);
@@ -850,7 +945,20 @@ __global__ void __launch_bounds__(kT, 1) k_ds_experts_down(SArgs a) {
         if (warp == kW - 3) { l2_prefetch(N.su_codes + (size_t)p0 * (E / 2), np * (E / 2), lane); l2_prefetch(reinterpret_cast<const unsigned char *>(N.su_bs) + (size_t)p0 * (E / 16), np * (E / 16), lane); }
     }
     /* unit u = slot * nj + row: slot-major, the order the parts land in. Each warp takes an equal share. */
-    {
+    if (NIT == 1 && n32 <= 4 * kMmaGroups && (a.flags & SP_STAGED_MMA_DN) && nj > 0) {
+        /* tile T = slot * tiles_per_slot + ti, slot-major (the order the parts land in), one tile per warp and turn */
+        const int tps = (nj + 15) >> 4;
+        int s = 0, ti = warp;
+#pragma unroll 1
+        while (ti >= tps) { ti -= tps; s++; }
+#pragma unroll 1
+        while (s < NU) {
+            down_tile_mma(sm, ly, ctl, a.s.status, s, ti, nj, njm, SGs, rb, sb, n32, blk16, lane, out);
+            ti += kW;
+#pragma unroll 1
+            while (ti >= tps) { ti -= tps; s++; }
+        }
+    } else {
         const int U = NU * nj;
         const int ua = (warp * U) / kW, ub = ((warp + 1) * U) / kW;
         int u = ua, s = nj > 0 ? ua / nj : 0, jj = ua - s * nj;          /* the one division of this kernel */
