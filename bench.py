@@ -308,6 +308,46 @@ def small_batch_leg(eng, NL, local_rank, rank, peak_gbs):
     return out
 
 
+# ---------------------------------------------------------------- where an expert-parallel layer's time goes
+def ep_stage_timing_leg(NL, PT, rank, local_rank, world, dist):
+    """CUDA-event stage times of one expert-parallel layer (the library loop, padded exchange, run eagerly: events
+    cannot be timed inside a graph replay). A second handle opened with SP_MOE_TIMING=1 carries the events, so the
+    headline handle stays untimed. Reported: rank 0's last layer, and the slowest rank's whole layer."""
+    import torch
+    from kairos_engine_b200 import FLAVOUR_PREFILL, MoeEngine, ep, synth
+    dev = f"cuda:{local_rank}"
+    Ml = PT // world
+    NLt = min(NL, 4)
+    os.environ["SP_MOE_TIMING"] = "1"
+    try:
+        eng = MoeEngine(n_layers=NLt, max_tokens=Ml, device=local_rank, max_expert_rows=PT * CFG["NU"], **CFG)
+    finally:
+        del os.environ["SP_MOE_TIMING"]
+    for L in range(NLt):
+        layer = synth.make_layer(CFG, 1000 * L, device=dev)
+        eng.upload_layer(L, layer, on_device=True)
+        del layer
+    x = synth.make_inputs(CFG, Ml, seed=99 + rank, device=dev)
+    cap = -(-13 * Ml * CFG["NU"] // (10 * world) // 8) * 8
+    epm = ep.NcclExpertParallel(eng, CFG, capacity_rows=cap, slices=1)
+    for _ in range(3):
+        epm.forward(x, 0, NLt, FLAVOUR_PREFILL)
+    torch.cuda.synchronize()
+    eng.status()
+    tm = epm.timing()
+    t = torch.tensor([tm["layer"]], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    epm.close()
+    eng.close()
+    torch.cuda.empty_cache()
+    out = {k + "_ms": round(v, 4) for k, v in tm.items()}
+    out["layer_ms_slowest_rank"] = round(float(t.item()), 4)
+    out["exchanges_share_of_layer"] = round((tm["gather_dispatch"] + tm["combine"]) / tm["layer"], 3) if tm["layer"] > 0 else None
+    out["note"] = ("last of %d layers, run eagerly (the timed pass above is a graph replay); gather_dispatch runs on the communication "
+                   "stream with the shared expert under it, so experts_after_dispatch is what the compute stream still had to do" % NLt)
+    return out
+
+
 # ---------------------------------------------------------------- prefill with fewer MMA terms per k-step
 def prefill_terms_leg(NL, PT, local_rank):
     """The same prefill pass with the weight rounded to fp16 (2 MMAs per k-step) and with the activation
@@ -600,6 +640,7 @@ def run_ours(args, rank, local_rank, world):
             zipf["router_bias"] = "zipf s=1.2 per-expert logit bias on every layer (seeded expert permutation)"
         for L in range(NL):
             eng.set_router_bias(L, bias)
+    stages = extra(ep_stage_timing_leg, NL, PT, rank, local_rank, world, dist) if (PT and world > 1 and args.ep_impl == "library") else None
     small = extra(small_batch_leg, eng, NL, local_rank, rank, peak) if (PT and world == 1) else None
     igemm = extra(int_gemm_leg, local_rank) if (PT and world == 1) else None
     terms = extra(prefill_terms_leg, NL, PT, local_rank) if (PT and world == 1) else None
@@ -626,6 +667,8 @@ def run_ours(args, rank, local_rank, world):
             line["prefill"] = prefill
         if zipf:
             line["zipf"] = zipf
+        if stages:
+            line["ep_stage_times"] = stages
         if small:
             line["small_batch"] = small
         if igemm:

@@ -178,6 +178,12 @@ int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, int rank, int
                           int M, const float *x_dev, float *y_dev, int capacity_rows, int slices, void *stream);
 /* rows this rank's experts processed in the last layer of the last sp_moe_ep_forward_dev call */
 long long sp_moe_ep_last_rows(const sp_moe *h);
+/* Stage times of the LAST layer of the most recent sp_moe_ep_forward_dev call, in milliseconds, from CUDA events:
+ * ms6[0] route (norms, router, top-NU, send buffer), [1] count gather + dispatch exchange, [2] end of the dispatch
+ * to end of the experts stage (the shared expert runs under the dispatch), [3] combine exchange, [4] finish,
+ * [5] the whole layer. Needs SP_MOE_TIMING=1 in the environment when the handle was opened, one token slice and
+ * a call made outside a stream capture; otherwise SP_MOE_EBADSTATE. Synchronises. */
+int sp_moe_ep_timing(sp_moe *h, float *ms6);
 /* Communicator helpers for callers without NCCL headers: 128 opaque bytes from one rank (ncclGetUniqueId), handed to
  * every rank by whatever channel the job has, then one communicator per rank on its current CUDA device. */
 int sp_moe_ep_unique_id(void *id128);

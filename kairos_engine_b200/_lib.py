@@ -16,7 +16,7 @@ EXPORTS = ("sp_last_error", "sp_set_error", "sp_moe_open", "sp_moe_close", "sp_m
            "sp_moe_ep_route_dev", "sp_moe_ep_recv_layout_dev", "sp_moe_ep_shared_dev", "sp_moe_ep_experts_dev", "sp_moe_ep_finish_dev",
            "sp_moe_ext_open", "sp_moe_ext_close", "sp_moe_ext_upload_experts", "sp_moe_ext_moe",
            "sp_frob_matmul_q8_dev", "sp_frob_matmul_q4_dev", "sp_moe_decode_timing", "sp_moe_debug_wait_timeout", "sp_moe_set_router_bias_dev", "sp_moe_load_sp_model",
-           "sp_moe_ep_forward_dev", "sp_moe_ep_last_rows", "sp_moe_ep_unique_id", "sp_moe_ep_comm_create", "sp_moe_ep_comm_destroy")
+           "sp_moe_ep_forward_dev", "sp_moe_ep_last_rows", "sp_moe_ep_timing", "sp_moe_ep_unique_id", "sp_moe_ep_comm_create", "sp_moe_ep_comm_destroy")
 
 
 class SpMoeConfig(C.Structure):
@@ -96,6 +96,8 @@ def lib():
         L.sp_moe_ep_forward_dev.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 6 + [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         L.sp_moe_ep_last_rows.argtypes = [C.c_void_p]
         L.sp_moe_ep_last_rows.restype = C.c_longlong
+        L.sp_moe_ep_timing.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
+        L.sp_moe_ep_timing.restype = C.c_int
         L.sp_moe_ep_unique_id.argtypes = [C.c_void_p]
         L.sp_moe_ep_comm_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
         L.sp_moe_ep_comm_destroy.argtypes = [C.c_void_p]

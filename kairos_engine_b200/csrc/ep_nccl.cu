@@ -106,6 +106,9 @@ struct EpState {
     int32_t *counts_host;                           /* page-locked, exact exchange */
     cudaStream_t comm;                              /* every NCCL call */
     long long last_rows;
+    bool timed;                                     /* SP_MOE_TIMING=1 at open: events carry time, begin/end bracket every layer */
+    cudaEvent_t begin, end;
+    bool timing_valid;                              /* the last call ran outside a stream capture with one slice */
 };
 
 void ep_free(void *p) {
@@ -114,6 +117,8 @@ void ep_free(void *p) {
     cudaSetDevice(s->device);
     if (s->comm) { cudaStreamSynchronize(s->comm); cudaStreamDestroy(s->comm); }
     for (auto &x : s->sl) for (cudaEvent_t e : {x.routed, x.gathered, x.dispatched, x.computed, x.combined}) if (e) cudaEventDestroy(e);
+    if (s->begin) cudaEventDestroy(s->begin);
+    if (s->end) cudaEventDestroy(s->end);
     if (s->base) cudaFree(s->base);
     if (s->counts_host) cudaFreeHost(s->counts_host);
     delete s;
@@ -129,6 +134,7 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
     if (!s) return fail(SP_MOE_ENOMEM, "sp_moe_ep_forward_dev: host OOM");
     memset(s, 0, sizeof *s);
     s->device = h->device; s->n_ranks = n_ranks; s->max_tokens = h->cfg.max_tokens; s->rows_cap = h->bs.max_rows;
+    s->timed = h->stamps != nullptr;                    /* the handle was opened with SP_MOE_TIMING=1 */
     const size_t E = h->cfg.E, NE = h->cfg.NE, NU = h->cfg.NU, MT = (size_t)s->max_tokens, R = (size_t)s->rows_cap;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     /* the slices share the token range and the row buffers: slice k of n uses its own part of each */
@@ -149,8 +155,9 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
         x.offsets = (int32_t *)(b + o_off) + (size_t)k * (NE + 1); x.row_index = (int32_t *)(b + o_ri);                  /* + row offset at use */
         x.send = (float *)(b + o_send); x.recv = (float *)(b + o_recv); x.out = (float *)(b + o_out); x.back = (float *)(b + o_back);
         for (cudaEvent_t *ev : {&x.routed, &x.gathered, &x.dispatched, &x.computed, &x.combined})
-            if (cudaEventCreateWithFlags(ev, cudaEventDisableTiming) != cudaSuccess) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
+            if (cudaEventCreateWithFlags(ev, s->timed ? cudaEventDefault : cudaEventDisableTiming) != cudaSuccess) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
     }
+    if (s->timed && (cudaEventCreate(&s->begin) != cudaSuccess || cudaEventCreate(&s->end) != cudaSuccess)) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
     if (cudaMallocHost((void **)&s->counts_host, 4 * NE * (size_t)n_ranks) != cudaSuccess || cudaStreamCreateWithFlags(&s->comm, cudaStreamNonBlocking) != cudaSuccess) {
         ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: stream / pinned buffer creation failed");
     }
@@ -227,11 +234,17 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
     int t0[kMaxSlices], tm[kMaxSlices]; size_t r0[kMaxSlices];
     for (int k = 0; k < ns; k++) { t0[k] = (int)((long long)M * k / ns); tm[k] = (int)((long long)M * (k + 1) / ns) - t0[k]; r0[k] = padded ? (size_t)k * n_ranks * cap : 0; }
 
+    bool timing = false;
+    if (s->timed && ns == 1) {
+        cudaStreamCaptureStatus cst = cudaStreamCaptureStatusNone;
+        timing = cudaStreamIsCapturing(st, &cst) == cudaSuccess && cst == cudaStreamCaptureStatusNone;
+    }
     const float *cur = x_dev;
     for (int li = 0; li < nl; li++) {
         const int L = lf + li;
         const SpLayerDev &W = h->layers_host[L];
         float *dst = (li == nl - 1) ? y_dev : ((li & 1) ? s->xb : s->xa);
+        if (timing && li == nl - 1) CK(cudaEventRecord(s->begin, st), "event record");
         if (padded) {
             /* ---- route every slice; its count gather and its dispatch follow on the communication stream */
             for (int k = 0; k < ns; k++) {
@@ -364,8 +377,31 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             CK(e, "finish");
             s->last_rows = R;
         }
+        if (timing && li == nl - 1) CK(cudaEventRecord(s->end, st), "event record");
         cur = dst;
     }
+    s->timing_valid = timing;
     h->launches += (uint64_t)nlaunch;
+    return SP_MOE_OK;
+}
+
+/* Stage times of the LAST layer of the most recent sp_moe_ep_forward_dev call, from CUDA events (handle opened
+ * with SP_MOE_TIMING=1, the call made outside a stream capture, one token slice): ms[0] route (norms, router,
+ * top-NU, send buffer), ms[1] count gather + dispatch exchange on the communication stream, ms[2] from the end of
+ * the dispatch to the end of the experts stage on the compute stream (the shared expert and the receive layout ran
+ * under the dispatch), ms[3] combine exchange, ms[4] finish, ms[5] the whole layer. Synchronises both streams. */
+extern "C" int sp_moe_ep_timing(sp_moe *h, float *ms6) {
+    if (!h || !ms6) return fail(SP_MOE_EBADARG, "sp_moe_ep_timing: NULL argument");
+    EpState *s = (EpState *)h->ep_state;
+    if (!s || !s->timed || !s->timing_valid) return fail(SP_MOE_EBADSTATE, "sp_moe_ep_timing: needs SP_MOE_TIMING=1 at open and a one-slice sp_moe_ep_forward_dev call outside a stream capture");
+    CK(cudaSetDevice(h->device), "cudaSetDevice");
+    CK(cudaEventSynchronize(s->end), "event synchronize");
+    const Slice &x = s->sl[0];
+    CK(cudaEventElapsedTime(ms6 + 0, s->begin, x.routed), "elapsed");
+    CK(cudaEventElapsedTime(ms6 + 1, x.routed, x.dispatched), "elapsed");
+    CK(cudaEventElapsedTime(ms6 + 2, x.dispatched, x.computed), "elapsed");
+    CK(cudaEventElapsedTime(ms6 + 3, x.computed, x.combined), "elapsed");
+    CK(cudaEventElapsedTime(ms6 + 4, x.combined, s->end), "elapsed");
+    CK(cudaEventElapsedTime(ms6 + 5, s->begin, s->end), "elapsed");
     return SP_MOE_OK;
 }

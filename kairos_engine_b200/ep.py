@@ -155,6 +155,16 @@ class NcclExpertParallel:
         from . import _lib
         return int(_lib.lib().sp_moe_ep_last_rows(self.engine._h))
 
+    def timing(self):
+        """Stage times (ms) of the last layer of the most recent forward(): needs SP_MOE_TIMING=1 when the engine was
+        opened, one slice and a call outside a stream capture."""
+        import ctypes as C
+        from . import _lib
+        ms = (C.c_float * 6)()
+        _lib.check(_lib.lib().sp_moe_ep_timing(self.engine._h, ms))
+        keys = ("route", "gather_dispatch", "experts_after_dispatch", "combine", "finish", "layer")
+        return {k: float(v) for k, v in zip(keys, ms)}
+
     def forward(self, x, layer_first=0, n_layers=1, flavour=1, out=None):
         from . import _lib
         y = torch.empty_like(x) if out is None else out

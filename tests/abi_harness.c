@@ -188,6 +188,13 @@ int main(void) {
                     CHECK(memcmp(y, y2, M * E * 4) == 0, "library loop on one rank == sp_moe_forward_dev, bit for bit (flavour %d, capacity %d)", flavour, cap);
                     CHECK(sp_moe_ep_last_rows(h) == (cap ? cap : M * NU), "sp_moe_ep_last_rows = %lld", sp_moe_ep_last_rows(h));
                 }
+            {
+                float ms6[6];
+                const int rc_t = sp_moe_ep_timing(h, ms6);          /* stage events carry time only when the handle was opened with SP_MOE_TIMING=1 */
+                if (getenv("SP_MOE_TIMING")) CHECK(rc_t == SP_MOE_OK && ms6[5] > 0.0f && ms6[0] >= 0.0f && ms6[4] >= 0.0f, "sp_moe_ep_timing (layer %.4f ms)", ms6[5]);
+                else CHECK(rc_t == SP_MOE_EBADSTATE, "sp_moe_ep_timing without SP_MOE_TIMING must be refused");
+                CHECK(sp_moe_ep_timing(h, NULL) == SP_MOE_EBADARG, "sp_moe_ep_timing must refuse NULL");
+            }
             CHECK(sp_moe_ep_forward_dev(h, comm, 3, 0, 0, NL, 0, M, x_dev, y_ep, 0, 1, st) == SP_MOE_EBADARG, "ep_forward must refuse n_ranks that does not divide NE");
             CHECK(sp_moe_ep_forward_dev(h, NULL, 1, 0, 0, NL, 0, M, x_dev, y_ep, 0, 1, st) == SP_MOE_EBADARG, "ep_forward must refuse a NULL communicator");
             if (comm) CHECK(sp_moe_ep_comm_destroy(comm) == SP_MOE_OK, "sp_moe_ep_comm_destroy");

@@ -189,7 +189,11 @@ def _nccl_rank(rank, world, port, cases, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         cfg, n_layers, M = orc.SMALL, 2, 24 + 8 * rank
-        eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, max_expert_rows=512, **cfg)
+        os.environ["SP_MOE_TIMING"] = "1"          # stage events carry time (sp_moe_ep_timing); nothing else changes
+        try:
+            eng = MoeEngine(n_layers=n_layers, max_tokens=64, device=rank, max_expert_rows=512, **cfg)
+        finally:
+            del os.environ["SP_MOE_TIMING"]
         for L in range(n_layers):
             eng.upload_layer(L, synth.make_layer(cfg, 77 + 1000 * L, rand_norms=True, device=f"cuda:{rank}"), on_device=True)
         x = torch.from_numpy(np.random.default_rng(rank).standard_normal((M, cfg["E"])).astype(np.float32)).cuda()
@@ -205,6 +209,9 @@ def _nccl_rank(rank, world, port, cases, q):
                 torch.cuda.synchronize()
                 ok = bool(torch.equal(got.view(torch.int32), want.view(torch.int32))) and bool(torch.equal(again.view(torch.int32), want.view(torch.int32)))
                 ok = ok and drv.last_rows > 0
+                if slices == 1:                    # the stage times of the last layer: positive, and they fit inside the layer
+                    tm = drv.timing()
+                    ok = ok and tm["layer"] > 0 and all(v >= 0 for v in tm.values()) and tm["route"] + tm["finish"] <= tm["layer"] * 1.001
                 drv.close()
             else:
                 got = ep.ExpertParallelMoe(eng, cfg, capacity_rows=capacity).forward(x, 0, n_layers, flavour)
