@@ -31,6 +31,7 @@
 #include <dlfcn.h>
 #include <mutex>
 #include <new>
+#include <vector>
 
 namespace {
 
@@ -39,12 +40,14 @@ typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;
 enum { ncclInt8 = 0, ncclInt32 = 2, ncclFloat32 = 7 };
+enum { ncclSum = 0, ncclMin = 3 };
 
 struct Nccl {
     ncclResult_t (*GetUniqueId)(ncclUniqueId *);
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
     ncclResult_t (*CommDestroy)(ncclComm_t);
     ncclResult_t (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t);      /* optional: only the peer-copy exchange needs it */
     ncclResult_t (*Send)(const void *, size_t, int, int, ncclComm_t, cudaStream_t);
     ncclResult_t (*Recv)(void *, size_t, int, int, ncclComm_t, cudaStream_t);
     ncclResult_t (*GroupStart)();
@@ -65,6 +68,7 @@ const Nccl *nccl() {
         g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))sym("ncclCommInitRank");
         g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))sym("ncclCommDestroy");
         g_nccl.AllGather = (decltype(g_nccl.AllGather))sym("ncclAllGather");
+        g_nccl.AllReduce = (decltype(g_nccl.AllReduce))sym("ncclAllReduce");
         g_nccl.Send = (decltype(g_nccl.Send))sym("ncclSend");
         g_nccl.Recv = (decltype(g_nccl.Recv))sym("ncclRecv");
         g_nccl.GroupStart = (decltype(g_nccl.GroupStart))sym("ncclGroupStart");
@@ -106,6 +110,12 @@ struct EpState {
     int32_t *counts_host;                           /* page-locked, exact exchange */
     cudaStream_t comm;                              /* every NCCL call */
     long long last_rows;
+    /* peer-copy exchange: every rank maps every other rank's arena (CUDA IPC) and pushes its blocks with device-to-device
+     * copies; NCCL then only carries the counts and a one-int all-reduce that tells a rank its blocks have landed */
+    int p2p;                                        /* 0 = not tried yet, 1 = in use, -1 = unavailable (NCCL send/recv instead) */
+    unsigned char *peer_base[64];
+    size_t o_recv, o_back;                          /* where recv / back sit in every rank's arena (same layout everywhere) */
+    int32_t *sync_dev;                              /* [4] ints for the landing all-reduce + 64 bytes per rank of IPC handles */
     bool timed;                                     /* SP_MOE_TIMING=1 at open: events carry time, begin/end bracket every layer */
     cudaEvent_t begin, end;
     bool timing_valid;                              /* the last call ran outside a stream capture with one slice */
@@ -117,6 +127,8 @@ void ep_free(void *p) {
     cudaSetDevice(s->device);
     if (s->comm) { cudaStreamSynchronize(s->comm); cudaStreamDestroy(s->comm); }
     for (auto &x : s->sl) for (cudaEvent_t e : {x.routed, x.gathered, x.dispatched, x.computed, x.combined}) if (e) cudaEventDestroy(e);
+    for (int r = 0; r < 64; r++) if (s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
+    if (s->sync_dev) cudaFree(s->sync_dev);
     if (s->begin) cudaEventDestroy(s->begin);
     if (s->end) cudaEventDestroy(s->end);
     if (s->base) cudaFree(s->base);
@@ -143,7 +155,7 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
     const size_t o_xa = take(4 * MT * E), o_xb = take(4 * MT * E), o_sel = take(4 * MT * NU), o_cw = take(4 * MT * NU), o_pi = take(4 * MT * NU);
     const size_t o_cnt = take(4 * NE * kMaxSlices), o_call = take(4 * NE * (size_t)n_ranks * kMaxSlices), o_off = take(4 * (NE + 1) * kMaxSlices), o_ri = take(4 * R);
     const size_t o_send = take(4 * R * E), o_recv = take(4 * R * E), o_out = take(4 * R * E), o_back = take(4 * R * E);
-    s->bytes = o;
+    s->bytes = o; s->o_recv = o_recv; s->o_back = o_back;
     cudaError_t e = cudaMalloc(&s->base, s->bytes);
     if (e != cudaSuccess) { delete s; return fail(SP_MOE_EBACKEND_OOM, "sp_moe_ep_forward_dev: exchange buffers (%lld MB): cuda error %lld", (long long)(o >> 20), (long long)e); }
     unsigned char *b = s->base;
@@ -164,6 +176,41 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
     h->ep_state = s; h->ep_state_free = ep_free;
     h->scratch_bytes += s->bytes;
     *out = s;
+    return SP_MOE_OK;
+}
+
+/* Maps every peer's exchange arena into this process (once per handle and world size, outside any stream capture).
+ * All ranks must end up in the same mode, so the outcome is agreed on with a min all-reduce. SP_MOE_EP_EXCHANGE=nccl
+ * keeps the NCCL send/recv exchange. */
+int ep_p2p_setup(EpState *s, const Nccl *N, ncclComm_t comm, int n_ranks, int rank) {
+    s->p2p = -1;
+    if (!N->AllReduce || n_ranks > 64) return SP_MOE_OK;
+    const char *ev = getenv("SP_MOE_EP_EXCHANGE");
+    int ok = !(ev && ev[0] == 'n');
+    if (cudaMalloc((void **)&s->sync_dev, 16 + 64 * (size_t)n_ranks) != cudaSuccess) { cudaGetLastError(); s->sync_dev = nullptr; return SP_MOE_OK; }
+    unsigned char *hd = reinterpret_cast<unsigned char *>(s->sync_dev) + 16;
+    cudaIpcMemHandle_t mine;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (cudaIpcGetMemHandle(&mine, s->base) != cudaSuccess) { cudaGetLastError(); ok = 0; memset(&mine, 0, sizeof mine); }
+    std::vector<cudaIpcMemHandle_t> all((size_t)n_ranks);
+    CK(cudaMemcpyAsync(hd + 64 * (size_t)rank, &mine, 64, cudaMemcpyHostToDevice, s->comm), "handle H2D");
+    NK(N->AllGather(hd + 64 * (size_t)rank, hd, 64, ncclInt8, comm, s->comm), "all-gather of the IPC handles");
+    CK(cudaMemcpyAsync(all.data(), hd, 64 * (size_t)n_ranks, cudaMemcpyDeviceToHost, s->comm), "handles D2H");
+    CK(cudaStreamSynchronize(s->comm), "stream synchronize");
+    for (int r = 0; r < n_ranks && ok; r++) {
+        if (r == rank) continue;
+        void *p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = 0; break; }
+        s->peer_base[r] = (unsigned char *)p;
+    }
+    int agreed = 0;
+    CK(cudaMemcpyAsync(s->sync_dev, &ok, 4, cudaMemcpyHostToDevice, s->comm), "flag H2D");
+    NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclMin, comm, s->comm), "all-reduce of the mode");
+    CK(cudaMemcpyAsync(&agreed, s->sync_dev + 1, 4, cudaMemcpyDeviceToHost, s->comm), "flag D2H");
+    CK(cudaStreamSynchronize(s->comm), "stream synchronize");
+    CK(cudaMemsetAsync(s->sync_dev, 0, 16, s->comm), "memset");
+    if (agreed == 1) s->p2p = 1;
+    else for (int r = 0; r < 64; r++) if (s->peer_base[r]) { cudaIpcCloseMemHandle(s->peer_base[r]); s->peer_base[r] = nullptr; }
     return SP_MOE_OK;
 }
 
@@ -234,6 +281,14 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
     int t0[kMaxSlices], tm[kMaxSlices]; size_t r0[kMaxSlices];
     for (int k = 0; k < ns; k++) { t0[k] = (int)((long long)M * k / ns); tm[k] = (int)((long long)M * (k + 1) / ns) - t0[k]; r0[k] = padded ? (size_t)k * n_ranks * cap : 0; }
 
+    if (s->p2p == 0) {                                    /* first call for this world: map the peers' buffers (not possible inside a capture) */
+        cudaStreamCaptureStatus cst = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cst) == cudaSuccess && cst == cudaStreamCaptureStatusNone) {
+            const int rc = ep_p2p_setup(s, N, comm, n_ranks, rank);
+            if (rc) return rc;
+        }
+    }
+    const bool p2p = s->p2p == 1;
     bool timing = false;
     if (s->timed && ns == 1) {
         cudaStreamCaptureStatus cst = cudaStreamCaptureStatusNone;
@@ -258,12 +313,20 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 CK(cudaStreamWaitEvent(cs, x.routed, 0), "event wait");
                 NK(N->AllGather(x.counts, x.counts_all, (size_t)NE, ncclInt32, comm, cs), "all-gather of the counts");
                 CK(cudaEventRecord(x.gathered, cs), "event record");
-                NK(N->GroupStart(), "group start");
-                for (int r = 0; r < n_ranks; r++) {
-                    NK(N->Send(x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch send");
-                    NK(N->Recv(x.recv + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                if (p2p) {                                    /* push block r into rank r's receive buffer, slot `rank`; then learn that every block has landed */
+                    for (int r = 0; r < n_ranks; r++) {
+                        float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_recv);
+                        CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
+                    }
+                    if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
+                } else {
+                    NK(N->GroupStart(), "group start");
+                    for (int r = 0; r < n_ranks; r++) {
+                        NK(N->Send(x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch send");
+                        NK(N->Recv(x.recv + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                    }
+                    NK(N->GroupEnd(), "group end");
                 }
-                NK(N->GroupEnd(), "group end");
                 CK(cudaEventRecord(x.dispatched, cs), "event record");
             }
             /* ---- per slice: the shared expert and the receive layout (under the dispatch), the experts, the combine */
@@ -282,12 +345,20 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 CK(e, "experts");
                 CK(cudaEventRecord(x.computed, st), "event record");
                 CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
-                NK(N->GroupStart(), "group start");
-                for (int r = 0; r < n_ranks; r++) {
-                    NK(N->Send(x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine send");
-                    NK(N->Recv(x.back + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine recv");
+                if (p2p) {
+                    for (int r = 0; r < n_ranks; r++) {
+                        float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_back);
+                        CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
+                    }
+                    if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
+                } else {
+                    NK(N->GroupStart(), "group start");
+                    for (int r = 0; r < n_ranks; r++) {
+                        NK(N->Send(x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine send");
+                        NK(N->Recv(x.back + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "combine recv");
+                    }
+                    NK(N->GroupEnd(), "group end");
                 }
-                NK(N->GroupEnd(), "group end");
                 CK(cudaEventRecord(x.combined, cs), "event record");
             }
             /* ---- finish every slice as its rows come back */
@@ -320,14 +391,28 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 send_n[r] = a; recv_n[r] = b2; R += b2;
             }
             if (R > s->rows_cap) return fail(SP_MOE_EBADARG, "sp_moe_ep_forward_dev: this rank would receive %lld rows, max_expert_rows is %d", R, s->rows_cap);
-            NK(N->GroupStart(), "group start");
-            { long long ro = 0; soff = 0;
-              for (int r = 0; r < n_ranks; r++) {
-                  if (send_n[r]) NK(N->Send(x.send + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "dispatch send");
-                  if (recv_n[r]) NK(N->Recv(x.recv + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "dispatch recv");
-                  soff += send_n[r]; ro += recv_n[r];
-              } }
-            NK(N->GroupEnd(), "group end");
+            /* rows rank a sends to rank b, from the gathered counts every rank holds */
+            auto rows_ab = [&](int a, int b2) { long long v = 0; for (int q = 0; q < epr; q++) v += s->counts_host[(size_t)a * NE + (size_t)b2 * epr + q]; return v; };
+            if (p2p) {                                        /* my block for rank r lands behind the blocks of the ranks before me */
+                soff = 0;
+                for (int r = 0; r < n_ranks; r++) {
+                    long long at = 0;
+                    for (int a = 0; a < rank; a++) at += rows_ab(a, r);
+                    float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_recv);
+                    if (send_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.send + (size_t)soff * E, (size_t)send_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
+                    soff += send_n[r];
+                }
+                if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
+            } else {
+                NK(N->GroupStart(), "group start");
+                { long long ro = 0; soff = 0;
+                  for (int r = 0; r < n_ranks; r++) {
+                      if (send_n[r]) NK(N->Send(x.send + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "dispatch send");
+                      if (recv_n[r]) NK(N->Recv(x.recv + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                      soff += send_n[r]; ro += recv_n[r];
+                  } }
+                NK(N->GroupEnd(), "group end");
+            }
             CK(cudaEventRecord(x.dispatched, cs), "event record");
             e = sp_batched_ep_shared(d, W, flavour, M, &h->bs, h->status, st, &nlk, 0, 0);
             nlaunch += nlk;
@@ -362,14 +447,26 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             }
             CK(cudaEventRecord(x.computed, st), "event record");
             CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
-            NK(N->GroupStart(), "group start");
-            { long long ro = 0; soff = 0;
-              for (int r = 0; r < n_ranks; r++) {
-                  if (recv_n[r]) NK(N->Send(x.out + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "combine send");
-                  if (send_n[r]) NK(N->Recv(x.back + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "combine recv");
-                  soff += send_n[r]; ro += recv_n[r];
-              } }
-            NK(N->GroupEnd(), "group end");
+            if (p2p) {                                        /* what came from rank r goes back to where r keeps the pairs it sent here */
+                long long ro = 0;
+                for (int r = 0; r < n_ranks; r++) {
+                    long long at = 0;
+                    for (int b2 = 0; b2 < rank; b2++) at += rows_ab(r, b2);
+                    float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_back);
+                    if (recv_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.out + (size_t)ro * E, (size_t)recv_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
+                    ro += recv_n[r];
+                }
+                if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
+            } else {
+                NK(N->GroupStart(), "group start");
+                { long long ro = 0; soff = 0;
+                  for (int r = 0; r < n_ranks; r++) {
+                      if (recv_n[r]) NK(N->Send(x.out + (size_t)ro * E, (size_t)recv_n[r] * E, ncclFloat32, r, comm, cs), "combine send");
+                      if (send_n[r]) NK(N->Recv(x.back + (size_t)soff * E, (size_t)send_n[r] * E, ncclFloat32, r, comm, cs), "combine recv");
+                      soff += send_n[r]; ro += recv_n[r];
+                  } }
+                NK(N->GroupEnd(), "group end");
+            }
             CK(cudaEventRecord(x.combined, cs), "event record");
             CK(cudaStreamWaitEvent(st, x.combined, 0), "event wait");
             e = sp_batched_ep_finish(d, W, M, cur, x.back, x.pair_index, dst, &h->bs, st, &nlk, 0, 0);
