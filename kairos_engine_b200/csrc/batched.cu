@@ -938,19 +938,24 @@ __global__ void __launch_bounds__(256) k_b_recv_layout(const int *counts_all, in
  *   finish  : ordered combine of the returned pair rows + the recombine.
  * The arithmetic of each pair is the single-GPU batched path's, so a split run is bit-identical. */
 /* the shared (always-on) expert of the tokens the last route call prepared: nx -> dn in the scratch */
+/* phase 0 = the whole shared expert; 1 = gate/up + GeGLU only (hd stays in the scratch); 2 = the down rows only */
 template <bool FA>
-cudaError_t ep_shared(const SpDims &d, const SpLayerDev &L, int M, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+cudaError_t ep_shared(const SpDims &d, const SpLayerDev &L, int M, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl, int phase) {
     const int E = d.E, FFS = d.FFS;
-    if (!FA && tc) return sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl);
+    if (!FA && tc) return sp_tc_shared_expert(tc, d, L, M, v.nx_f, v.dn, status, st, nl, phase);
     GroupArgs g{};
-    g.M = M;
-    g.codes = L.sg_codes; g.bs = L.sg_bs; g.ucodes = L.su_codes; g.ubs = L.su_bs;
-    g.in = E; g.rows = FFS; g.act_div = 1; g.q = v.nx_q; g.sx = v.nx_s; g.corr = v.nx_c; g.xf = v.nx_f; g.out = v.hd; g.out_stride = FFS;
-    launch_rows<FA, true>(g, 1, st, nl);
-    if (FA) { k_b_quant_rows<<<M, 256, 0, st>>>(v.hd, FFS, v.hd_q, v.hd_s, v.hd_c); (*nl)++; }
-    g.codes = L.sd_codes; g.bs = L.sd_bs; g.ucodes = nullptr; g.ubs = nullptr;
-    g.in = FFS; g.rows = E; g.q = v.hd_q; g.sx = v.hd_s; g.corr = v.hd_c; g.xf = v.hd; g.out = v.dn; g.out_stride = E;
-    launch_rows<FA, false>(g, 1, st, nl);
+    g.M = M; g.act_div = 1;
+    if (phase != 2) {
+        g.codes = L.sg_codes; g.bs = L.sg_bs; g.ucodes = L.su_codes; g.ubs = L.su_bs;
+        g.in = E; g.rows = FFS; g.q = v.nx_q; g.sx = v.nx_s; g.corr = v.nx_c; g.xf = v.nx_f; g.out = v.hd; g.out_stride = FFS;
+        launch_rows<FA, true>(g, 1, st, nl);
+        if (FA) { k_b_quant_rows<<<M, 256, 0, st>>>(v.hd, FFS, v.hd_q, v.hd_s, v.hd_c); (*nl)++; }
+    }
+    if (phase != 1) {
+        g.codes = L.sd_codes; g.bs = L.sd_bs; g.ucodes = nullptr; g.ubs = nullptr;
+        g.in = FFS; g.rows = E; g.q = v.hd_q; g.sx = v.hd_s; g.corr = v.hd_c; g.xf = v.hd; g.out = v.dn; g.out_stride = E;
+        launch_rows<FA, false>(g, 1, st, nl);
+    }
     return cudaGetLastError();
 }
 
@@ -973,7 +978,7 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
     e = cudaMemcpyAsync(cw, v.cw, (size_t)4 * M * NU, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return e;
     if (defer_shared) return cudaGetLastError();
-    return ep_shared<FA>(d, L, M, v, tc, status, st, nl);
+    return ep_shared<FA>(d, L, M, v, tc, status, st, nl, 0);
 }
 
 template <bool FA>
@@ -1013,11 +1018,11 @@ cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all
     k_b_recv_layout<<<1, 256, (size_t)(3 * nb + 1) * sizeof(int), st>>>(counts_all, d.NE, n_ranks, rank, capacity, offsets, row_index);
     return cudaGetLastError();
 }
-cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0, int slice) {
+cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0, int slice, int phase) {
     *nlaunch = 0;
-    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices) return cudaErrorInvalidValue;
+    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices || phase < 0 || phase > 2) return cudaErrorInvalidValue;
     BView v = bview_slice(d, s, t0, slice);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_shared<true>(d, L, M, v, s->tc, status, st, nlaunch) : ep_shared<false>(d, L, M, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_shared<true>(d, L, M, v, s->tc, status, st, nlaunch, phase) : ep_shared<false>(d, L, M, v, s->tc, status, st, nlaunch, phase);
 }
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {

@@ -39,7 +39,8 @@ cudaError_t sp_batched_ep_route(const SpDims &d, const SpLayerDev &L, int flavou
 cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all, int n_ranks, int rank, int capacity, int32_t *offsets, int32_t *row_index,
                                       cudaStream_t st, int *nlaunch);
 /* the shared expert of the tokens the last route call prepared, when that call deferred it */
-cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);
+/* phase: 0 = the whole shared expert, 1 = gate/up + GeGLU only, 2 = the down rows only (after a phase-1 call for the same tokens) */
+cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0, int phase = 0);
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
                                   float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,

@@ -109,6 +109,8 @@ struct EpState {
     Slice sl[kMaxSlices];
     int32_t *counts_host;                           /* page-locked, exact exchange */
     cudaStream_t comm;                              /* every NCCL call */
+    cudaStream_t local;                             /* peer-copy exchange: this rank's own block, beside the copies to the peers */
+    cudaEvent_t fork, joined;
     long long last_rows;
     /* peer-copy exchange: every rank maps every other rank's arena (CUDA IPC) and pushes its blocks with device-to-device
      * copies; NCCL then only carries the counts and a one-int all-reduce that tells a rank its blocks have landed */
@@ -129,6 +131,9 @@ void ep_free(void *p) {
     for (auto &x : s->sl) for (cudaEvent_t e : {x.routed, x.gathered, x.dispatched, x.computed, x.combined}) if (e) cudaEventDestroy(e);
     for (int r = 0; r < 64; r++) if (s->peer_base[r]) cudaIpcCloseMemHandle(s->peer_base[r]);
     if (s->sync_dev) cudaFree(s->sync_dev);
+    if (s->fork) cudaEventDestroy(s->fork);
+    if (s->joined) cudaEventDestroy(s->joined);
+    if (s->local) cudaStreamDestroy(s->local);
     if (s->begin) cudaEventDestroy(s->begin);
     if (s->end) cudaEventDestroy(s->end);
     if (s->base) cudaFree(s->base);
@@ -170,7 +175,9 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
             if (cudaEventCreateWithFlags(ev, s->timed ? cudaEventDefault : cudaEventDisableTiming) != cudaSuccess) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
     }
     if (s->timed && (cudaEventCreate(&s->begin) != cudaSuccess || cudaEventCreate(&s->end) != cudaSuccess)) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
-    if (cudaMallocHost((void **)&s->counts_host, 4 * NE * (size_t)n_ranks) != cudaSuccess || cudaStreamCreateWithFlags(&s->comm, cudaStreamNonBlocking) != cudaSuccess) {
+    if (cudaMallocHost((void **)&s->counts_host, 4 * NE * (size_t)n_ranks) != cudaSuccess || cudaStreamCreateWithFlags(&s->comm, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&s->local, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s->joined, cudaEventDisableTiming) != cudaSuccess) {
         ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: stream / pinned buffer creation failed");
     }
     h->ep_state = s; h->ep_state_free = ep_free;
@@ -289,6 +296,16 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
         }
     }
     const bool p2p = s->p2p == 1;
+    /* this rank's own block: a copy on a stream of its own, forked from the communication stream before the copies to
+     * the peers are queued there and joined back after them, so that it runs beside them */
+    auto own_fork = [&](float *dstp, const float *srcp, size_t bytes) -> cudaError_t {
+        cudaError_t e2 = cudaEventRecord(s->fork, s->comm);
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(s->local, s->fork, 0);
+        if (e2 == cudaSuccess && bytes) e2 = cudaMemcpyAsync(dstp, srcp, bytes, cudaMemcpyDeviceToDevice, s->local);
+        if (e2 == cudaSuccess) e2 = cudaEventRecord(s->joined, s->local);
+        return e2;
+    };
+    auto own_join = [&]() -> cudaError_t { return cudaStreamWaitEvent(s->comm, s->joined, 0); };
     bool timing = false;
     if (s->timed && ns == 1) {
         cudaStreamCaptureStatus cst = cudaStreamCaptureStatusNone;
@@ -314,10 +331,13 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 NK(N->AllGather(x.counts, x.counts_all, (size_t)NE, ncclInt32, comm, cs), "all-gather of the counts");
                 CK(cudaEventRecord(x.gathered, cs), "event record");
                 if (p2p) {                                    /* push block r into rank r's receive buffer, slot `rank`; then learn that every block has landed */
+                    CK(own_fork(x.recv + (r0[k] + (size_t)rank * cap) * E, x.send + (r0[k] + (size_t)rank * cap) * E, (size_t)cap * E * 4), "own block");
                     for (int r = 0; r < n_ranks; r++) {
-                        float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_recv);
+                        if (r == rank) continue;
+                        float *dstb = reinterpret_cast<float *>(s->peer_base[r] + s->o_recv);
                         CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
                     }
+                    CK(own_join(), "own block");
                     if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
                 } else {
                     NK(N->GroupStart(), "group start");
@@ -332,10 +352,13 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             /* ---- per slice: the shared expert and the receive layout (under the dispatch), the experts, the combine */
             for (int k = 0; k < ns; k++) {
                 Slice &x = s->sl[k];
-                cudaError_t e = sp_batched_ep_shared(d, W, flavour, tm[k], &h->bs, h->status, st, &nlk, t0[k], k);
+                /* the counts first (a tiny collective that must not queue behind a GEMM that fills every SM), then the
+                 * shared expert under the dispatch. With one slice only its gate/up half goes here and its down half
+                 * runs under the combine; with more slices the halves would share one hidden-vector scratch. */
+                CK(cudaStreamWaitEvent(st, x.gathered, 0), "event wait");
+                cudaError_t e = sp_batched_ep_shared(d, W, flavour, tm[k], &h->bs, h->status, st, &nlk, t0[k], k, ns == 1 ? 1 : 0);
                 nlaunch += nlk;
                 CK(e, "shared expert");
-                CK(cudaStreamWaitEvent(st, x.gathered, 0), "event wait");
                 e = sp_batched_ep_recv_layout(d, x.counts_all, n_ranks, rank, cap, x.offsets, x.row_index + r0[k], st, &nlk);
                 nlaunch += nlk;
                 CK(e, "receive layout");
@@ -344,12 +367,20 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 nlaunch += nlk;
                 CK(e, "experts");
                 CK(cudaEventRecord(x.computed, st), "event record");
+                if (ns == 1) {                                /* the shared expert's down rows, under the combine */
+                    e = sp_batched_ep_shared(d, W, flavour, tm[k], &h->bs, h->status, st, &nlk, t0[k], k, 2);
+                    nlaunch += nlk;
+                    CK(e, "shared expert (down)");
+                }
                 CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
                 if (p2p) {
+                    CK(own_fork(x.back + (r0[k] + (size_t)rank * cap) * E, x.out + (r0[k] + (size_t)rank * cap) * E, (size_t)cap * E * 4), "own block");
                     for (int r = 0; r < n_ranks; r++) {
-                        float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_back);
+                        if (r == rank) continue;
+                        float *dstb = reinterpret_cast<float *>(s->peer_base[r] + s->o_back);
                         CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
                     }
+                    CK(own_join(), "own block");
                     if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
                 } else {
                     NK(N->GroupStart(), "group start");
@@ -414,7 +445,7 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 NK(N->GroupEnd(), "group end");
             }
             CK(cudaEventRecord(x.dispatched, cs), "event record");
-            e = sp_batched_ep_shared(d, W, flavour, M, &h->bs, h->status, st, &nlk, 0, 0);
+            e = sp_batched_ep_shared(d, W, flavour, M, &h->bs, h->status, st, &nlk, 0, 0, 1);      /* gate/up under the dispatch, down under the combine */
             nlaunch += nlk;
             CK(e, "shared expert");
             /* the rows arrive source-major, each source's block sorted by expert: the layout kernel with a capacity
@@ -446,6 +477,9 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 CK(e, "experts");
             }
             CK(cudaEventRecord(x.computed, st), "event record");
+            e = sp_batched_ep_shared(d, W, flavour, M, &h->bs, h->status, st, &nlk, 0, 0, 2);
+            nlaunch += nlk;
+            CK(e, "shared expert (down)");
             CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
             if (p2p) {                                        /* what came from rank r goes back to where r keeps the pairs it sent here */
                 long long ro = 0;

@@ -425,20 +425,24 @@ void launch_gemm(const SpTcPlan *p, const TcArgs &a, const TcMaps &maps, cudaStr
 }  // namespace
 
 cudaError_t sp_tc_shared_expert(SpTcPlan *p, const SpDims &d, const SpLayerDev &L, int M, const float *nx, float *dn,
-                                int *status, cudaStream_t st, int *nl) {
+                                int *status, cudaStream_t st, int *nl, int phase) {
     if (!p || M > p->Mcap) return cudaErrorInvalidValue;
-    k_tc_split<<<M, 256, 0, st>>>(nx, nullptr, d.E, p->nx_hi, p->nx_lo); (*nl)++;
-    k_tc_plan<<<1, 1024, 0, st>>>(nullptr, 1, M, M, p->tiles_sh, p->ntiles_sh, p->cap_sh); (*nl)++;
-    TcArgs a{};
-    a.codes[0] = L.sg_codes; a.bs[0] = L.sg_bs; a.codes[1] = L.su_codes; a.bs[1] = L.su_bs;
-    a.group_rows = 0; a.acc1_off = 0; a.rows = d.FFS; a.K = d.E; a.tiles = p->tiles_sh; a.n_tiles = p->ntiles_sh;
-    a.m_tiles = (d.FFS + 127) / 128; a.out_hi = p->hd_hi; a.out_lo = p->hd_lo; a.out_k = d.FFS; a.status = status;
-    launch_gemm<true>(p, a, p->m_nx, st, nl);
-    TcArgs b{};
-    b.codes[0] = b.codes[1] = L.sd_codes; b.bs[0] = b.bs[1] = L.sd_bs;
-    b.group_rows = 0; b.rows = d.E; b.K = d.FFS; b.tiles = p->tiles_sh; b.n_tiles = p->ntiles_sh;
-    b.m_tiles = (d.E + 255) / 256; b.out_f = dn; b.out_stride = d.E; b.rowmap = nullptr; b.status = status;
-    launch_gemm<false>(p, b, p->m_hd, st, nl);
+    if (phase != 2) {                                     /* gate/up + GeGLU -> hd (split fp16), kept in the plan's scratch */
+        k_tc_split<<<M, 256, 0, st>>>(nx, nullptr, d.E, p->nx_hi, p->nx_lo); (*nl)++;
+        k_tc_plan<<<1, 1024, 0, st>>>(nullptr, 1, M, M, p->tiles_sh, p->ntiles_sh, p->cap_sh); (*nl)++;
+        TcArgs a{};
+        a.codes[0] = L.sg_codes; a.bs[0] = L.sg_bs; a.codes[1] = L.su_codes; a.bs[1] = L.su_bs;
+        a.group_rows = 0; a.acc1_off = 0; a.rows = d.FFS; a.K = d.E; a.tiles = p->tiles_sh; a.n_tiles = p->ntiles_sh;
+        a.m_tiles = (d.FFS + 127) / 128; a.out_hi = p->hd_hi; a.out_lo = p->hd_lo; a.out_k = d.FFS; a.status = status;
+        launch_gemm<true>(p, a, p->m_nx, st, nl);
+    }
+    if (phase != 1) {                                     /* down: hd -> dn (the tile table of the first phase is still in place) */
+        TcArgs b{};
+        b.codes[0] = b.codes[1] = L.sd_codes; b.bs[0] = b.bs[1] = L.sd_bs;
+        b.group_rows = 0; b.rows = d.E; b.K = d.FFS; b.tiles = p->tiles_sh; b.n_tiles = p->ntiles_sh;
+        b.m_tiles = (d.E + 255) / 256; b.out_f = dn; b.out_stride = d.E; b.rowmap = nullptr; b.status = status;
+        launch_gemm<false>(p, b, p->m_hd, st, nl);
+    }
     return cudaGetLastError();
 }
 

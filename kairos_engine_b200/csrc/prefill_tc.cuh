@@ -12,7 +12,7 @@ void sp_tc_destroy(SpTcPlan *p);
 
 /* shared expert: nx [M][E] f32 (normalised input) -> dn [M][E] f32 = Wd . geglu(Wg nx, Wu nx) */
 cudaError_t sp_tc_shared_expert(SpTcPlan *p, const SpDims &d, const SpLayerDev &L, int M, const float *nx, float *dn,
-                                int *status, cudaStream_t st, int *nl);
+                                int *status, cudaStream_t st, int *nl, int phase = 0);
 /* routed experts on R rows sorted by expert (expert e owns rows [offsets[e], offsets[e+1]), device
  * array of NE+1 ints): out[rowmap ? rowmap[r] : r][E] = Wdn[e] . geglu(Wgu[e] . rows[r]).
  * gather != NULL: row r is src[gather[r]] instead of src[r]. R <= max_rows. */
