@@ -20,9 +20,20 @@
  * CUDA graph; a block that does not fit is reported by sp_moe_status. Exact (capacity_rows == 0): the split
  * sizes are read on the host once per layer (one slice, no overlap).
  *
+ * How the rows travel. NCCL send/recv pairs by default. In a world of two ranks (or with SP_MOE_EP_EXCHANGE=copy)
+ * every rank maps the other ranks' exchange buffers through CUDA IPC once, pushes its blocks with plain
+ * device-to-device copies (copy engines: no SM is taken from the GEMMs that run beside them) and a one-int
+ * all-reduce tells each rank that its blocks have landed. A buffer is only overwritten after its reader is
+ * done: a rank's dispatch of layer L+1 follows its finish of layer L, which needed every peer's combine of
+ * layer L, which followed that peer's experts stage - the last reader of the buffer the dispatch writes; the
+ * combine's buffer is protected the same way by the dispatch of the same layer.
+ * With one token slice the shared expert is split around the experts stage: its gate/up GEMM runs under the
+ * dispatch, its down GEMM under the combine.
+ *
  * NCCL is not linked: its entry points are looked up at run time (the copy the process already holds - e.g. the
  * one a framework loaded - or libnccl.so.2 from the loader's path), so a daemon that never runs
- * expert-parallel needs no NCCL at all. No load uses cluster multicast; peers are reached through NCCL only.
+ * expert-parallel needs no NCCL at all. No load uses cluster multicast; a peer's memory is only ever the
+ * destination of a device-to-device copy.
  */
 #include "handle.cuh"
 #include <cstdarg>
@@ -187,13 +198,15 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
 }
 
 /* Maps every peer's exchange arena into this process (once per handle and world size, outside any stream capture).
- * All ranks must end up in the same mode, so the outcome is agreed on with a min all-reduce. SP_MOE_EP_EXCHANGE=nccl
- * keeps the NCCL send/recv exchange. */
+ * All ranks must end up in the same mode, so the outcome is agreed on with a min all-reduce. */
 int ep_p2p_setup(EpState *s, const Nccl *N, ncclComm_t comm, int n_ranks, int rank) {
     s->p2p = -1;
     if (!N->AllReduce || n_ranks > 64) return SP_MOE_OK;
+    /* measured on B200 / NVSwitch: with one peer a copy engine moves a block at ~750 GB/s against ~310 GB/s for an NCCL
+     * send/recv pair (2 GPUs: 69.8 K -> 89.2 K tokens/s); with three or more peers NCCL's concurrent pairs win
+     * (4 GPUs: 132 K against 120 K). So: copies for a world of two, NCCL otherwise; SP_MOE_EP_EXCHANGE=copy|nccl overrides. */
     const char *ev = getenv("SP_MOE_EP_EXCHANGE");
-    int ok = !(ev && ev[0] == 'n');
+    int ok = ev && ev[0] == 'c' ? 1 : (ev && ev[0] == 'n' ? 0 : (n_ranks <= 2 ? 1 : 0));
     if (cudaMalloc((void **)&s->sync_dev, 16 + 64 * (size_t)n_ranks) != cudaSuccess) { cudaGetLastError(); s->sync_dev = nullptr; return SP_MOE_OK; }
     unsigned char *hd = reinterpret_cast<unsigned char *>(s->sync_dev) + 16;
     cudaIpcMemHandle_t mine;
