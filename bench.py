@@ -39,10 +39,10 @@ TOKENS_PER_STEP = 256
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the three decode kernels of one layer, from one ncu capture of a
 # 2-layer stack (six launches = one token; L2 flushed before each kernel, prefetch hints off):
-#   SP_MOE_STAGED_FLAGS=0 ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:k_ds_ -s 18 -c 6
+#   SP_MOE_STAGED_FLAGS=8 ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:k_ds_ -s 18 -c 6
 #       python bench.py --steps 1 --warmup 3 --tokens-per-step 1 --layers 2 --no-cpu --no-prefill
-# 38,507,392 B per layer against 38,331,904 algorithmic; the traffic is the same for every layer, so a launch is 30x that.
-NCU_TRAFFIC_BYTES_PER_LAYER = 38507392
+# 38,520,832 B per layer against 38,331,904 algorithmic; the traffic is the same for every layer, so a launch is 30x that.
+NCU_TRAFFIC_BYTES_PER_LAYER = 38520832
 
 
 def measured_peaks():
