@@ -395,6 +395,7 @@ struct GroupArgs {
     int up_off;                                    /* PAIR: row offset of the up row */
     const uint8_t *ucodes; const uint16_t *ubs;    /* PAIR with a separate up tensor (shared expert), else NULL */
     int act_div;                                   /* activation row = item / act_div (NU for routed gate|up, 1 otherwise) */
+    const int *act_index;                          /* with offset: sorted position -> activation row, when it is not the item's own row (NULL = item / act_div) */
     /* flavour A */
     const signed char *q; const float *sx; const int *corr;
     /* flavour B */
@@ -486,7 +487,7 @@ __global__ void __launch_bounds__(256) k_b_rows(GroupArgs g) {
     const int b16 = g.in >> 4;
     for (int i = 0; i < cnt; i++) {
         const int item = list ? list[i] : (g.index ? g.index[first + i] : first + i);
-        const size_t arow = (size_t)(item / g.act_div);
+        const size_t arow = (size_t)(g.act_index ? g.act_index[first + i] : item / g.act_div);
         float o;
         if (FA) {
             const int4 *q = reinterpret_cast<const int4 *>(g.q + arow * g.in);
@@ -627,7 +628,7 @@ __global__ void __launch_bounds__(256, 2) k_b_rows_mma(GroupArgs g) {
             if (t < nb) {
                 const int item = list ? list[b0 + t] : (g.index ? g.index[first + b0 + t] : first + b0 + t);
                 if (hw == 0 && lane == 0) items[t] = item;
-                const size_t arow = (size_t)(item / g.act_div);
+                const size_t arow = (size_t)(g.act_index ? g.act_index[first + b0 + t] : item / g.act_div);
                 const signed char *qs = g.q + arow * in;
                 unsigned char *pd = P + (size_t)t * pstride;
                 for (int k = lane + 32 * hw; k < b16; k += 64) cp_async16(pd + 16 * k, qs + 16 * (size_t)k);
@@ -880,9 +881,66 @@ __global__ void __launch_bounds__(256) k_b_dispatch_rows(const float *in_f, cons
         pos = owner * capacity + in_block;
     }
     if (threadIdx.x == 0) pair_index[p] = pos;
+    if (!rows) return;                           /* positions only: the caller sends token rows instead of pair rows */
     const float4 *src = reinterpret_cast<const float4 *>(in_f + (size_t)(p / NU) * E);
     float4 *dst = reinterpret_cast<float4 *>(rows + (size_t)pos * E);
     for (int i = threadIdx.x; i < E / 4; i += 256) dst[i] = src[i];
+}
+/* ---- token dispatch: a token's input row goes to a destination rank once, however many of its NU experts live
+ * there. Per destination r: the tokens with at least one expert on r, in token order (slot = rank among them), up to
+ * cap_tokens rows; per pair (at its position in the padded pair order, pair_index) the slot of its token. The receiver
+ * multiplies row  source * cap_tokens + slot  for the pair. */
+__global__ void __launch_bounds__(1024) k_b_tok_scan(const int *sel_asc, int M, int NU, int epr, int n_ranks, int cap_tokens, int *slot, int *status) {
+    __shared__ int wsum[32];
+    __shared__ int carry;
+    const int r = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    if (t == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < M; base += 1024) {
+        const int tok = base + t;
+        int flag = 0;
+        if (tok < M) for (int k = 0; k < NU; k++) flag |= (sel_asc[tok * NU + k] / epr == r);
+        const unsigned bal = __ballot_sync(0xffffffffu, flag);
+        const int within = __popc(bal & ((1u << lane) - 1u));
+        if (lane == 0) wsum[warp] = __popc(bal);
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; w++) before += wsum[w];
+        if (tok < M) {
+            const int sl = before + within;
+            slot[tok * n_ranks + r] = flag ? sl : -1;
+            if (flag && sl >= cap_tokens) atomicExch(status, SP_KERR_OVERFLOW);
+        }
+        __syncthreads();
+        if (t == 0) { int tot = 0; for (int w = 0; w < 32; w++) tot += wsum[w]; carry += tot; }
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(256) k_b_tok_rows(const float *in_f, const int *slot, int n_ranks, int cap_tokens, int E, float *tokrows) {
+    const int tok = blockIdx.x, r = blockIdx.y;
+    const int sl = slot[tok * n_ranks + r];
+    if (sl < 0 || sl >= cap_tokens) return;
+    const float4 *src = reinterpret_cast<const float4 *>(in_f + (size_t)tok * E);
+    float4 *dst = reinterpret_cast<float4 *>(tokrows + ((size_t)r * cap_tokens + sl) * E);
+    for (int i = threadIdx.x; i < E / 4; i += 256) dst[i] = src[i];
+}
+__global__ void __launch_bounds__(256) k_b_tok_idx(const int *sel_asc, const int *pair_index, const int *slot, int np, int NU, int epr, int n_ranks, int cap_tokens, int *tokidx) {
+    const int p = blockIdx.x * 256 + threadIdx.x;
+    if (p >= np) return;
+    const int r = sel_asc[p] / epr;
+    int sl = slot[(p / NU) * n_ranks + r];
+    sl = sl < 0 ? 0 : (sl >= cap_tokens ? cap_tokens - 1 : sl);
+    tokidx[pair_index[p]] = sl;
+}
+/* receiver: sorted position p -> the row of the pair's token among the token rows that arrived */
+__global__ void __launch_bounds__(256) k_b_in_index(const int *row_index, const int *tokidx_recv, int n, int capacity, int cap_tokens, int n_ranks, int *in_index) {
+    const int p = blockIdx.x * 256 + threadIdx.x;
+    if (p >= n) return;
+    const int a = row_index[p];                              /* arrival slot of the pair: source * capacity + position in the source's block */
+    const int src = a / capacity;
+    int sl = tokidx_recv[a];
+    sl = sl < 0 ? 0 : (sl >= cap_tokens ? cap_tokens - 1 : sl);
+    in_index[p] = (src < n_ranks ? src : n_ranks - 1) * cap_tokens + sl;
 }
 /* what a rank received through the padded exchange: source s's block starts at row s * capacity and holds
  * its rows for this rank's experts, sorted by expert. counts_all[s][e] = pairs of expert e on rank s.
@@ -981,20 +1039,22 @@ cudaError_t ep_route(const SpDims &d, const SpLayerDev &L, int M, const float *x
     return ep_shared<FA>(d, L, M, v, tc, status, st, nl, 0);
 }
 
+/* in_index (optional, with n_in input rows): sorted position -> input row, when several pairs share one input row
+ * (token dispatch); the outputs still go to the pair's own row (row_index). */
 template <bool FA>
 cudaError_t ep_experts(const SpDims &d, const SpLayerDev &L, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets, float *rows_out,
-                       BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
+                       const int32_t *in_index, int n_in, BView &v, SpTcPlan *tc, int *status, cudaStream_t st, int *nl) {
     const int E = d.E, NE = d.NE, FFE = d.FFE;
     if (R == 0) return cudaSuccess;
-    if (!FA && tc) return sp_tc_routed(tc, d, L, R, rows_in, row_index, offsets, row_index, rows_out, status, st, nl);
-    if (FA) { k_b_quant_rows<<<R, 256, 0, st>>>(rows_in, E, v.ep_q, v.ep_s, v.ep_c); (*nl)++; }
+    if (!FA && tc) return sp_tc_routed(tc, d, L, R, rows_in, in_index ? in_index : row_index, offsets, row_index, rows_out, status, st, nl);
+    if (FA) { k_b_quant_rows<<<in_index ? n_in : R, 256, 0, st>>>(rows_in, E, v.ep_q, v.ep_s, v.ep_c); (*nl)++; }
     GroupArgs g{};
-    g.M = R; g.offset = offsets; g.index = row_index;
+    g.M = R; g.offset = offsets; g.index = row_index; g.act_index = in_index;
     g.codes = L.gu_codes; g.bs = L.gu_bs; g.rows_per_group = 2LL * FFE;
     g.in = E; g.rows = FFE; g.up_off = FFE; g.act_div = 1; g.q = v.ep_q; g.sx = v.ep_s; g.corr = v.ep_c; g.xf = rows_in; g.out = v.h; g.out_stride = FFE;
     launch_rows<FA, true>(g, NE, st, nl);
     if (FA) { k_b_quant_rows<<<R, 256, 0, st>>>(v.h, FFE, v.h_q, v.h_s, v.h_c); (*nl)++; }
-    g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E;
+    g.codes = L.dn_codes; g.bs = L.dn_bs; g.rows_per_group = E; g.act_index = nullptr;          /* h has one row per pair */
     g.in = FFE; g.rows = E; g.q = v.h_q; g.sx = v.h_s; g.corr = v.h_c; g.xf = v.h; g.out = rows_out; g.out_stride = E;
     launch_rows<FA, false>(g, NE, st, nl);
     return cudaGetLastError();
@@ -1025,12 +1085,34 @@ cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavo
     return flavour == SP_MOE_FLAVOUR_DECODE ? ep_shared<true>(d, L, M, v, s->tc, status, st, nlaunch, phase) : ep_shared<false>(d, L, M, v, s->tc, status, st, nlaunch, phase);
 }
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
-                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch) {
+                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, const int32_t *in_index, int n_in) {
     *nlaunch = 0;
-    if (!s->base || R > s->max_rows) return cudaErrorInvalidValue;
+    if (!s->base || R > s->max_rows || (in_index && (n_in <= 0 || n_in > s->max_rows))) return cudaErrorInvalidValue;
     BView v = bview(d, s);
-    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, row_index, offsets, rows_out, v, s->tc, status, st, nlaunch)
-                                            : ep_experts<false>(d, L, R, rows_in, row_index, offsets, rows_out, v, s->tc, status, st, nlaunch);
+    return flavour == SP_MOE_FLAVOUR_DECODE ? ep_experts<true>(d, L, R, rows_in, row_index, offsets, rows_out, in_index, n_in, v, s->tc, status, st, nlaunch)
+                                            : ep_experts<false>(d, L, R, rows_in, row_index, offsets, rows_out, in_index, n_in, v, s->tc, status, st, nlaunch);
+}
+/* token dispatch, sender side (after sp_batched_ep_route of the same tokens with rows == NULL): tokrows
+ * [n_ranks][cap_tokens][E], tokidx [n_ranks][capacity] (the pair order of the padded exchange), slot = scratch of
+ * M * n_ranks ints */
+cudaError_t sp_batched_ep_tokens(const SpDims &d, int M, int n_ranks, int capacity, int cap_tokens, const int32_t *sel_asc, const int32_t *pair_index,
+                                 float *tokrows, int32_t *tokidx, int32_t *slot, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0, int slice) {
+    *nlaunch = 0;
+    if (!s->base || t0 < 0 || t0 + M > s->max_tokens || slice < 0 || slice >= kSlices || n_ranks <= 0 || d.NE % n_ranks || capacity <= 0 || cap_tokens <= 0) return cudaErrorInvalidValue;
+    BView v = bview_slice(d, s, t0, slice);
+    const int epr = d.NE / n_ranks;
+    k_b_tok_scan<<<n_ranks, 1024, 0, st>>>(sel_asc, M, d.NU, epr, n_ranks, cap_tokens, slot, status); (*nlaunch)++;
+    k_b_tok_rows<<<dim3((unsigned)M, (unsigned)n_ranks), 256, 0, st>>>(v.in_f, slot, n_ranks, cap_tokens, d.E, tokrows); (*nlaunch)++;
+    k_b_tok_idx<<<(M * d.NU + 255) / 256, 256, 0, st>>>(sel_asc, pair_index, slot, M * d.NU, d.NU, epr, n_ranks, cap_tokens, tokidx); (*nlaunch)++;
+    return cudaGetLastError();
+}
+/* token dispatch, receiver side (after sp_batched_ep_recv_layout): in_index[n_ranks * capacity] */
+cudaError_t sp_batched_ep_in_index(const int32_t *row_index, const int32_t *tokidx_recv, int n_ranks, int capacity, int cap_tokens, int32_t *in_index,
+                                   cudaStream_t st, int *nlaunch) {
+    *nlaunch = 1;
+    const int n = n_ranks * capacity;
+    k_b_in_index<<<(n + 255) / 256, 256, 0, st>>>(row_index, tokidx_recv, n, capacity, cap_tokens, n_ranks, in_index);
+    return cudaGetLastError();
 }
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,
                                  SpBatchedScratch *s, cudaStream_t st, int *nlaunch, int t0, int slice) {

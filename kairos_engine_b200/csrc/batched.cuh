@@ -42,6 +42,13 @@ cudaError_t sp_batched_ep_recv_layout(const SpDims &d, const int32_t *counts_all
 /* phase: 0 = the whole shared expert, 1 = gate/up + GeGLU only, 2 = the down rows only (after a phase-1 call for the same tokens) */
 cudaError_t sp_batched_ep_shared(const SpDims &d, const SpLayerDev &L, int flavour, int M, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0, int phase = 0);
 cudaError_t sp_batched_ep_experts(const SpDims &d, const SpLayerDev &L, int flavour, int R, const float *rows_in, const int32_t *row_index, const int32_t *offsets,
-                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch);
+                                  float *rows_out, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch,
+                                  const int32_t *in_index = nullptr, int n_in = 0);   /* in_index: sorted position -> input row when pairs share input rows */
+/* token dispatch (each token's input row travels once per destination rank): sender side after a route call made with
+ * rows == NULL, and the receiver's input index after the receive layout */
+cudaError_t sp_batched_ep_tokens(const SpDims &d, int M, int n_ranks, int capacity, int cap_tokens, const int32_t *sel_asc, const int32_t *pair_index,
+                                 float *tokrows, int32_t *tokidx, int32_t *slot, SpBatchedScratch *s, int *status, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);
+cudaError_t sp_batched_ep_in_index(const int32_t *row_index, const int32_t *tokidx_recv, int n_ranks, int capacity, int cap_tokens, int32_t *in_index,
+                                   cudaStream_t st, int *nlaunch);
 cudaError_t sp_batched_ep_finish(const SpDims &d, const SpLayerDev &L, int M, const float *x, const float *pair_rows, const int32_t *pair_index, float *y,
                                  SpBatchedScratch *s, cudaStream_t st, int *nlaunch, int t0 = 0, int slice = 0);

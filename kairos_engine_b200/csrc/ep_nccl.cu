@@ -111,6 +111,7 @@ constexpr int kMaxSlices = SP_BATCHED_MAX_SLICES;
 struct Slice {                      /* everything one token slice keeps between its stages */
     int32_t *sel_asc, *counts, *pair_index, *counts_all, *offsets, *row_index;
     float *cw, *send, *recv, *out, *back;
+    int32_t *ti_send, *ti_recv, *slot, *in_index;   /* token dispatch: per-pair token slots (sent / received), scan scratch, the receiver's input index */
     cudaEvent_t routed, gathered, dispatched, computed, combined;
 };
 struct EpState {
@@ -127,7 +128,8 @@ struct EpState {
      * copies; NCCL then only carries the counts and a one-int all-reduce that tells a rank its blocks have landed */
     int p2p;                                        /* 0 = not tried yet, 1 = in use, -1 = unavailable (NCCL send/recv instead) */
     unsigned char *peer_base[64];
-    size_t o_recv, o_back;                          /* where recv / back sit in every rank's arena (same layout everywhere) */
+    size_t o_recv, o_back, o_tir;                   /* where recv / back / ti_recv sit in every rank's arena (same layout everywhere) */
+    int token_dispatch;                             /* padded exchange: each token's row travels once per destination (SP_MOE_EP_DISPATCH=rows switches it off) */
     int32_t *sync_dev;                              /* [4] ints for the landing all-reduce + 64 bytes per rank of IPC handles */
     bool timed;                                     /* SP_MOE_TIMING=1 at open: events carry time, begin/end bracket every layer */
     cudaEvent_t begin, end;
@@ -171,7 +173,9 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
     const size_t o_xa = take(4 * MT * E), o_xb = take(4 * MT * E), o_sel = take(4 * MT * NU), o_cw = take(4 * MT * NU), o_pi = take(4 * MT * NU);
     const size_t o_cnt = take(4 * NE * kMaxSlices), o_call = take(4 * NE * (size_t)n_ranks * kMaxSlices), o_off = take(4 * (NE + 1) * kMaxSlices), o_ri = take(4 * R);
     const size_t o_send = take(4 * R * E), o_recv = take(4 * R * E), o_out = take(4 * R * E), o_back = take(4 * R * E);
-    s->bytes = o; s->o_recv = o_recv; s->o_back = o_back;
+    const size_t o_tis = take(4 * R), o_tir = take(4 * R), o_slot = take(4 * MT * (size_t)n_ranks), o_ii = take(4 * R);
+    s->bytes = o; s->o_recv = o_recv; s->o_back = o_back; s->o_tir = o_tir;
+    { const char *dv = getenv("SP_MOE_EP_DISPATCH"); s->token_dispatch = !(dv && dv[0] == 'r'); }
     cudaError_t e = cudaMalloc(&s->base, s->bytes);
     if (e != cudaSuccess) { delete s; return fail(SP_MOE_EBACKEND_OOM, "sp_moe_ep_forward_dev: exchange buffers (%lld MB): cuda error %lld", (long long)(o >> 20), (long long)e); }
     unsigned char *b = s->base;
@@ -182,6 +186,7 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
         x.counts = (int32_t *)(b + o_cnt) + (size_t)k * NE; x.counts_all = (int32_t *)(b + o_call) + (size_t)k * NE * n_ranks;
         x.offsets = (int32_t *)(b + o_off) + (size_t)k * (NE + 1); x.row_index = (int32_t *)(b + o_ri);                  /* + row offset at use */
         x.send = (float *)(b + o_send); x.recv = (float *)(b + o_recv); x.out = (float *)(b + o_out); x.back = (float *)(b + o_back);
+        x.ti_send = (int32_t *)(b + o_tis); x.ti_recv = (int32_t *)(b + o_tir); x.slot = (int32_t *)(b + o_slot); x.in_index = (int32_t *)(b + o_ii);   /* + row / token offset at use */
         for (cudaEvent_t *ev : {&x.routed, &x.gathered, &x.dispatched, &x.computed, &x.combined})
             if (cudaEventCreateWithFlags(ev, s->timed ? cudaEventDefault : cudaEventDisableTiming) != cudaSuccess) { ep_free(s); return fail(SP_MOE_ECUDA, "sp_moe_ep_forward_dev: event creation failed"); }
     }
@@ -309,12 +314,17 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
         }
     }
     const bool p2p = s->p2p == 1;
+    /* token dispatch (padded exchange): a destination never gets more distinct tokens than this rank may hold, so blocks
+     * of min(capacity, max_tokens) token rows cannot overflow; every rank derives the same size from the shared config */
+    const bool tokd = padded && s->token_dispatch;
+    const int capT = tokd ? (cap < (c.max_tokens + 7) / 8 * 8 ? cap : (c.max_tokens + 7) / 8 * 8) : 0;
     /* this rank's own block: a copy on a stream of its own, forked from the communication stream before the copies to
      * the peers are queued there and joined back after them, so that it runs beside them */
-    auto own_fork = [&](float *dstp, const float *srcp, size_t bytes) -> cudaError_t {
+    auto own_fork = [&](void *dstp, const void *srcp, size_t bytes, void *dst2 = nullptr, const void *src2 = nullptr, size_t bytes2 = 0) -> cudaError_t {
         cudaError_t e2 = cudaEventRecord(s->fork, s->comm);
         if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(s->local, s->fork, 0);
         if (e2 == cudaSuccess && bytes) e2 = cudaMemcpyAsync(dstp, srcp, bytes, cudaMemcpyDeviceToDevice, s->local);
+        if (e2 == cudaSuccess && bytes2) e2 = cudaMemcpyAsync(dst2, src2, bytes2, cudaMemcpyDeviceToDevice, s->local);
         if (e2 == cudaSuccess) e2 = cudaEventRecord(s->joined, s->local);
         return e2;
     };
@@ -335,28 +345,42 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             for (int k = 0; k < ns; k++) {
                 Slice &x = s->sl[k];
                 cudaError_t e = sp_batched_ep_route(d, W, flavour, tm[k], cur + (size_t)t0[k] * E, x.sel_asc + (size_t)t0[k] * NU, x.cw + (size_t)t0[k] * NU,
-                                                    x.send + r0[k] * E, x.counts, x.pair_index + (size_t)t0[k] * NU, nullptr, nullptr, 1, n_ranks, cap,
+                                                    tokd ? nullptr : x.send + r0[k] * E, x.counts, x.pair_index + (size_t)t0[k] * NU, nullptr, nullptr, 1, n_ranks, cap,
                                                     &h->bs, h->status, st, &nlk, t0[k], k);
                 nlaunch += nlk;
                 CK(e, "route");
+                if (tokd) {                                   /* token rows per destination + every pair's token slot, instead of one row per pair */
+                    e = sp_batched_ep_tokens(d, tm[k], n_ranks, cap, capT, x.sel_asc + (size_t)t0[k] * NU, x.pair_index + (size_t)t0[k] * NU, x.send + r0[k] * E,
+                                             x.ti_send + r0[k], x.slot + (size_t)t0[k] * n_ranks, &h->bs, h->status, st, &nlk, t0[k], k);
+                    nlaunch += nlk;
+                    CK(e, "token dispatch");
+                }
                 CK(cudaEventRecord(x.routed, st), "event record");
                 CK(cudaStreamWaitEvent(cs, x.routed, 0), "event wait");
                 NK(N->AllGather(x.counts, x.counts_all, (size_t)NE, ncclInt32, comm, cs), "all-gather of the counts");
                 CK(cudaEventRecord(x.gathered, cs), "event record");
+                const size_t drows = tokd ? (size_t)capT : (size_t)cap;      /* rows per destination block of the dispatch */
                 if (p2p) {                                    /* push block r into rank r's receive buffer, slot `rank`; then learn that every block has landed */
-                    CK(own_fork(x.recv + (r0[k] + (size_t)rank * cap) * E, x.send + (r0[k] + (size_t)rank * cap) * E, (size_t)cap * E * 4), "own block");
+                    CK(own_fork(x.recv + (r0[k] + rank * drows) * E, x.send + (r0[k] + rank * drows) * E, drows * E * 4,
+                                x.ti_recv + r0[k] + (size_t)rank * cap, x.ti_send + r0[k] + (size_t)rank * cap, tokd ? (size_t)cap * 4 : 0), "own block");
                     for (int r = 0; r < n_ranks; r++) {
                         if (r == rank) continue;
                         float *dstb = reinterpret_cast<float *>(s->peer_base[r] + s->o_recv);
-                        CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
+                        CK(cudaMemcpyAsync(dstb + (r0[k] + rank * drows) * E, x.send + (r0[k] + r * drows) * E, drows * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
+                        if (tokd) CK(cudaMemcpyAsync(reinterpret_cast<int32_t *>(s->peer_base[r] + s->o_tir) + r0[k] + (size_t)rank * cap, x.ti_send + r0[k] + (size_t)r * cap,
+                                                     (size_t)cap * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy (slots)");
                     }
                     CK(own_join(), "own block");
                     if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
                 } else {
                     NK(N->GroupStart(), "group start");
                     for (int r = 0; r < n_ranks; r++) {
-                        NK(N->Send(x.send + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch send");
-                        NK(N->Recv(x.recv + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                        NK(N->Send(x.send + (r0[k] + r * drows) * E, drows * E, ncclFloat32, r, comm, cs), "dispatch send");
+                        NK(N->Recv(x.recv + (r0[k] + r * drows) * E, drows * E, ncclFloat32, r, comm, cs), "dispatch recv");
+                        if (tokd) {
+                            NK(N->Send(x.ti_send + r0[k] + (size_t)r * cap, (size_t)cap, ncclInt32, r, comm, cs), "dispatch send (slots)");
+                            NK(N->Recv(x.ti_recv + r0[k] + (size_t)r * cap, (size_t)cap, ncclInt32, r, comm, cs), "dispatch recv (slots)");
+                        }
                     }
                     NK(N->GroupEnd(), "group end");
                 }
@@ -376,7 +400,13 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 nlaunch += nlk;
                 CK(e, "receive layout");
                 CK(cudaStreamWaitEvent(st, x.dispatched, 0), "event wait");
-                e = sp_batched_ep_experts(d, W, flavour, n_ranks * cap, x.recv + r0[k] * E, x.row_index + r0[k], x.offsets, x.out + r0[k] * E, &h->bs, h->status, st, &nlk);
+                if (tokd) {
+                    e = sp_batched_ep_in_index(x.row_index + r0[k], x.ti_recv + r0[k], n_ranks, cap, capT, x.in_index + r0[k], st, &nlk);
+                    nlaunch += nlk;
+                    CK(e, "input index");
+                }
+                e = sp_batched_ep_experts(d, W, flavour, n_ranks * cap, x.recv + r0[k] * E, x.row_index + r0[k], x.offsets, x.out + r0[k] * E, &h->bs, h->status, st, &nlk,
+                                          tokd ? x.in_index + r0[k] : nullptr, tokd ? n_ranks * capT : 0);
                 nlaunch += nlk;
                 CK(e, "experts");
                 CK(cudaEventRecord(x.computed, st), "event record");
