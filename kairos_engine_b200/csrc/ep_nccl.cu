@@ -30,6 +30,12 @@
  * With one token slice the shared expert is split around the experts stage: its gate/up GEMM runs under the
  * dispatch, its down GEMM under the combine.
  *
+ * What the dispatch carries. In the padded exchange a token's input row goes to a destination rank once, however
+ * many of its NU experts live there (blocks of min(capacity, max_tokens) token rows, which cannot overflow), with
+ * a 4-byte slot per pair in the padded pair order; the receiver turns the slots into a gather index for its GEMMs'
+ * input rows and still writes one output row per pair (SP_MOE_EP_DISPATCH=rows sends one row per pair instead).
+ * The exact exchange sends one row per pair.
+ *
  * NCCL is not linked: its entry points are looked up at run time (the copy the process already holds - e.g. the
  * one a framework loaded - or libnccl.so.2 from the loader's path), so a daemon that never runs
  * expert-parallel needs no NCCL at all. No load uses cluster multicast; a peer's memory is only ever the

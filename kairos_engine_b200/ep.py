@@ -128,11 +128,13 @@ class ExpertParallelMoe:
 
 
 class NcclExpertParallel:
-    """The same loop run inside the library (sp_moe_ep_forward_dev): NCCL called from C++, exchanges on an internal
-    stream under the expert GEMMs of other token slices. torch.distributed is used once, to hand rank 0's NCCL id
-    to the other ranks; the communicator is the library's own."""
+    """The same loop run inside the library (sp_moe_ep_forward_dev): NCCL called from C++, the exchanges on an internal
+    stream beside the GEMMs (the shared expert's two halves run under the dispatch and the combine; with a padded
+    exchange a token's row travels once per destination rank; in a world of two ranks the rows move by device-to-device
+    copies into IPC-mapped peer buffers). torch.distributed is used once, to hand rank 0's NCCL id to the other
+    ranks; the communicator is the library's own. Every rank must open its engine with the same configuration."""
 
-    def __init__(self, engine, cfg, group=None, capacity_rows=0, slices=2):
+    def __init__(self, engine, cfg, group=None, capacity_rows=0, slices=1):
         import ctypes as C
         from . import _lib
         self.engine, self.cfg = engine, cfg
