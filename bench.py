@@ -11,9 +11,12 @@ replicas for the decode metric (decode does not shard); the expert-parallel pref
 is reported in the `prefill` object, and the load-imbalance stress in `zipf`.
 
 Beside the headline the line carries: `parity` (results checked against the CPU checker and
-against the library's own second path, outside every timed region), `prefill`, `small_batch`,
-`int_gemm`, `cpu_baseline`, `ref_gpu_kernels` (the reference's own decode kernels, compiled for this
-GPU, timed on the same shapes).
+against the library's own second path, outside every timed region), `prefill`, `small_batch`
+(M = 4..64 in the decode arithmetic, roofline with the measured number of distinct experts),
+`prefill_terms` (the opt-in 2- and 1-term GEMM modes beside the exact default), `int_gemm`,
+`cpu_baseline`, `ref_gpu_kernels` (the reference's own decode kernels, compiled for this GPU, timed
+on the same shapes); at N>1 `zipf` and `ep_stage_times` (CUDA-event times of the stages of one
+expert-parallel layer: route, dispatch, experts, combine, finish).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
