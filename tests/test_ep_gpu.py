@@ -178,8 +178,10 @@ def _free_port():
     return p
 
 
-def _nccl_rank(rank, world, port, cases, q):
-    """cases: list of (impl, flavour, capacity, slices). One process pair, one NCCL start-up, every case."""
+def _nccl_rank(rank, world, port, cases, q, env=None):
+    """cases: list of (impl, flavour, capacity, slices). One process pair, one NCCL start-up, every case.
+    env: switches the library reads when the handle's expert-parallel state is first built."""
+    os.environ.update(env or {})
     import torch
     import torch.distributed as dist
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -225,7 +227,7 @@ def _nccl_rank(rank, world, port, cases, q):
         dist.destroy_process_group()
 
 
-def _run_pair(cases):
+def _run_pair(cases, env=None):
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -233,7 +235,7 @@ def _run_pair(cases):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, cases, q)) for r in range(2)]
+    ps = [ctx.Process(target=_nccl_rank, args=(r, 2, port, cases, q, env)) for r in range(2)]
     for p in ps: p.start()
     got = [q.get(timeout=600) for _ in ps]
     for p in ps:
@@ -249,7 +251,19 @@ def test_two_gpus_nccl_equal_single_gpu():
     _run_pair([("torch", A, 0, 1), ("torch", B, 0, 1), ("torch", A, 160, 1), ("torch", B, 160, 1)])
 
 
+LIBRARY_CASES = [("library", B, 0, 1), ("library", A, 0, 1), ("library", B, 160, 1), ("library", B, 160, 2), ("library", A, 160, 3), ("library", B, 200, 4)]
+
+
 def test_two_gpus_library_loop_equals_single_gpu():
     """sp_moe_ep_forward_dev (the whole loop behind the C ABI, its own NCCL communicator) == the single-GPU pass,
-    bit for bit: exact and padded exchange, one to four token slices in flight."""
-    _run_pair([("library", B, 0, 1), ("library", A, 0, 1), ("library", B, 160, 1), ("library", B, 160, 2), ("library", A, 160, 3), ("library", B, 200, 4)])
+    bit for bit: exact and padded exchange, one to four token slices in flight. In a world of two ranks the rows move
+    by device-to-device copies into the peer's buffers, and the padded exchange sends token rows."""
+    _run_pair(LIBRARY_CASES)
+
+
+@pytest.mark.parametrize("env", [{"SP_MOE_EP_EXCHANGE": "nccl"}, {"SP_MOE_EP_EXCHANGE": "nccl", "SP_MOE_EP_DISPATCH": "rows"},
+                                 {"SP_MOE_EP_EXCHANGE": "copy", "SP_MOE_EP_DISPATCH": "rows"}])
+def test_two_gpus_library_loop_other_exchanges(env):
+    """The same cases with the rows moved by NCCL send/recv pairs (what a world of more than two ranks uses), and with
+    one row per (token, expert) pair instead of token rows."""
+    _run_pair(LIBRARY_CASES, env)
