@@ -20,7 +20,7 @@
  * CUDA graph; a block that does not fit is reported by sp_moe_status. Exact (capacity_rows == 0): the split
  * sizes are read on the host once per layer (one slice, no overlap).
  *
- * How the rows travel. NCCL send/recv pairs by default. In a world of two ranks (or with SP_MOE_EP_EXCHANGE=copy)
+ * How the rows travel. NCCL send/recv pairs in a world of more than four ranks. Up to four (or with SP_MOE_EP_EXCHANGE=copy)
  * every rank maps the other ranks' exchange buffers through CUDA IPC once, pushes its blocks with plain
  * device-to-device copies (copy engines: no SM is taken from the GEMMs that run beside them) and a one-int
  * all-reduce tells each rank that its blocks have landed. A buffer is only overwritten after its reader is
@@ -213,11 +213,14 @@ int ep_ensure(sp_moe *h, int n_ranks, EpState **out) {
 int ep_p2p_setup(EpState *s, const Nccl *N, ncclComm_t comm, int n_ranks, int rank) {
     s->p2p = -1;
     if (!N->AllReduce || n_ranks > 64) return SP_MOE_OK;
-    /* measured on B200 / NVSwitch: with one peer a copy engine moves a block at ~750 GB/s against ~310 GB/s for an NCCL
-     * send/recv pair (2 GPUs: 69.8 K -> 89.2 K tokens/s); with three or more peers NCCL's concurrent pairs win
-     * (4 GPUs: 132 K against 120 K). So: copies for a world of two, NCCL otherwise; SP_MOE_EP_EXCHANGE=copy|nccl overrides. */
+    /* measured on B200 / NVSwitch, 4096 tokens: a copy engine moves a block at ~750 GB/s against ~310 GB/s for an NCCL
+     * send/recv pair, but the copies of one rank are queued one after the other (destinations staggered so that every rank
+     * receives one copy at a time) and a one-int all-reduce follows them. 2 GPUs: 69.8 K -> 80.3 K tokens/s with copies;
+     * 4 GPUs: 0.865 against 0.972 ms per layer; 8 GPUs: 0.704 against 0.594 ms per layer (seven small copies and the
+     * all-reduce cost more than NCCL's concurrent pairs). So: copies up to four ranks, NCCL beyond;
+     * SP_MOE_EP_EXCHANGE=copy|nccl overrides. */
     const char *ev = getenv("SP_MOE_EP_EXCHANGE");
-    int ok = ev && ev[0] == 'c' ? 1 : (ev && ev[0] == 'n' ? 0 : (n_ranks <= 2 ? 1 : 0));
+    int ok = ev && ev[0] == 'c' ? 1 : (ev && ev[0] == 'n' ? 0 : (n_ranks <= 4 ? 1 : 0));
     if (cudaMalloc((void **)&s->sync_dev, 16 + 64 * (size_t)n_ranks) != cudaSuccess) { cudaGetLastError(); s->sync_dev = nullptr; return SP_MOE_OK; }
     unsigned char *hd = reinterpret_cast<unsigned char *>(s->sync_dev) + 16;
     cudaIpcMemHandle_t mine;
@@ -369,8 +372,8 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 if (p2p) {                                    /* push block r into rank r's receive buffer, slot `rank`; then learn that every block has landed */
                     CK(own_fork(x.recv + (r0[k] + rank * drows) * E, x.send + (r0[k] + rank * drows) * E, drows * E * 4,
                                 x.ti_recv + r0[k] + (size_t)rank * cap, x.ti_send + r0[k] + (size_t)rank * cap, tokd ? (size_t)cap * 4 : 0), "own block");
-                    for (int r = 0; r < n_ranks; r++) {
-                        if (r == rank) continue;
+                    for (int i = 1; i < n_ranks; i++) {           /* rank + 1, rank + 2, ...: at every step each rank is the destination of exactly one copy */
+                        const int r = (rank + i) % n_ranks;
                         float *dstb = reinterpret_cast<float *>(s->peer_base[r] + s->o_recv);
                         CK(cudaMemcpyAsync(dstb + (r0[k] + rank * drows) * E, x.send + (r0[k] + r * drows) * E, drows * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
                         if (tokd) CK(cudaMemcpyAsync(reinterpret_cast<int32_t *>(s->peer_base[r] + s->o_tir) + r0[k] + (size_t)rank * cap, x.ti_send + r0[k] + (size_t)r * cap,
@@ -424,8 +427,8 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
                 CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
                 if (p2p) {
                     CK(own_fork(x.back + (r0[k] + (size_t)rank * cap) * E, x.out + (r0[k] + (size_t)rank * cap) * E, (size_t)cap * E * 4), "own block");
-                    for (int r = 0; r < n_ranks; r++) {
-                        if (r == rank) continue;
+                    for (int i = 1; i < n_ranks; i++) {
+                        const int r = (rank + i) % n_ranks;
                         float *dstb = reinterpret_cast<float *>(s->peer_base[r] + s->o_back);
                         CK(cudaMemcpyAsync(dstb + (r0[k] + (size_t)rank * cap) * E, x.out + (r0[k] + (size_t)r * cap) * E, (size_t)cap * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
                     }
@@ -474,13 +477,13 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             /* rows rank a sends to rank b, from the gathered counts every rank holds */
             auto rows_ab = [&](int a, int b2) { long long v = 0; for (int q = 0; q < epr; q++) v += s->counts_host[(size_t)a * NE + (size_t)b2 * epr + q]; return v; };
             if (p2p) {                                        /* my block for rank r lands behind the blocks of the ranks before me */
-                soff = 0;
-                for (int r = 0; r < n_ranks; r++) {
-                    long long at = 0;
+                for (int i = 0; i < n_ranks; i++) {               /* own block first, then rank + 1, rank + 2, ...: one copy per destination at a time */
+                    const int r = (rank + i) % n_ranks;
+                    long long at = 0, from = 0;
                     for (int a = 0; a < rank; a++) at += rows_ab(a, r);
+                    for (int b2 = 0; b2 < r; b2++) from += send_n[b2];
                     float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_recv);
-                    if (send_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.send + (size_t)soff * E, (size_t)send_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
-                    soff += send_n[r];
+                    if (send_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.send + (size_t)from * E, (size_t)send_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "dispatch copy");
                 }
                 if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
             } else {
@@ -531,13 +534,13 @@ extern "C" int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, in
             CK(e, "shared expert (down)");
             CK(cudaStreamWaitEvent(cs, x.computed, 0), "event wait");
             if (p2p) {                                        /* what came from rank r goes back to where r keeps the pairs it sent here */
-                long long ro = 0;
-                for (int r = 0; r < n_ranks; r++) {
-                    long long at = 0;
+                for (int i = 0; i < n_ranks; i++) {
+                    const int r = (rank + i) % n_ranks;
+                    long long at = 0, from = 0;
                     for (int b2 = 0; b2 < rank; b2++) at += rows_ab(r, b2);
+                    for (int a = 0; a < r; a++) from += recv_n[a];
                     float *dstb = reinterpret_cast<float *>((r == rank ? s->base : s->peer_base[r]) + s->o_back);
-                    if (recv_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.out + (size_t)ro * E, (size_t)recv_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
-                    ro += recv_n[r];
+                    if (recv_n[r]) CK(cudaMemcpyAsync(dstb + (size_t)at * E, x.out + (size_t)from * E, (size_t)recv_n[r] * E * 4, cudaMemcpyDeviceToDevice, cs), "combine copy");
                 }
                 if (n_ranks > 1) NK(N->AllReduce(s->sync_dev, s->sync_dev + 1, 1, ncclInt32, ncclSum, comm, cs), "landing all-reduce");
             } else {

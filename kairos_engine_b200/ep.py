@@ -130,7 +130,7 @@ class ExpertParallelMoe:
 class NcclExpertParallel:
     """The same loop run inside the library (sp_moe_ep_forward_dev): NCCL called from C++, the exchanges on an internal
     stream beside the GEMMs (the shared expert's two halves run under the dispatch and the combine; with a padded
-    exchange a token's row travels once per destination rank; in a world of two ranks the rows move by device-to-device
+    exchange a token's row travels once per destination rank; in a world of up to four ranks the rows move by device-to-device
     copies into IPC-mapped peer buffers). torch.distributed is used once, to hand rank 0's NCCL id to the other
     ranks; the communicator is the library's own. Every rank must open its engine with the same configuration."""
 

@@ -256,7 +256,7 @@ LIBRARY_CASES = [("library", B, 0, 1), ("library", A, 0, 1), ("library", B, 160,
 
 def test_two_gpus_library_loop_equals_single_gpu():
     """sp_moe_ep_forward_dev (the whole loop behind the C ABI, its own NCCL communicator) == the single-GPU pass,
-    bit for bit: exact and padded exchange, one to four token slices in flight. In a world of two ranks the rows move
+    bit for bit: exact and padded exchange, one to four token slices in flight. In a world of up to four ranks the rows move
     by device-to-device copies into the peer's buffers, and the padded exchange sends token rows."""
     _run_pair(LIBRARY_CASES)
 
@@ -264,6 +264,6 @@ def test_two_gpus_library_loop_equals_single_gpu():
 @pytest.mark.parametrize("env", [{"SP_MOE_EP_EXCHANGE": "nccl"}, {"SP_MOE_EP_EXCHANGE": "nccl", "SP_MOE_EP_DISPATCH": "rows"},
                                  {"SP_MOE_EP_EXCHANGE": "copy", "SP_MOE_EP_DISPATCH": "rows"}])
 def test_two_gpus_library_loop_other_exchanges(env):
-    """The same cases with the rows moved by NCCL send/recv pairs (what a world of more than two ranks uses), and with
+    """The same cases with the rows moved by NCCL send/recv pairs (what a world of more than four ranks uses), and with
     one row per (token, expert) pair instead of token rows."""
     _run_pair(LIBRARY_CASES, env)
