@@ -187,3 +187,49 @@ def test_world_must_divide_experts():
         pass
     with pytest.raises(Exception):
         ep.ExpertParallelMoe(FakeStages(CFG), dict(CFG, NE=7))
+
+
+def test_token_dispatch_protocol():
+    """The padded exchange's token dispatch, restated on the host (what k_b_tok_scan / k_b_tok_rows / k_b_tok_idx do on
+    the sender and k_b_in_index on the receiver): a token's row travels once per destination rank, every pair carries
+    the slot of its token, and the receiver's gather index picks, for every pair, exactly the row a one-row-per-pair
+    exchange would have delivered."""
+    cfg = dict(E=8, NE=16, NU=4)
+    world, M = 4, 23
+    epr, NU = cfg["NE"] // world, cfg["NU"]
+    cap, cap_t = 48, 24                                       # pairs / token rows per destination block
+    g = torch.Generator().manual_seed(5)
+    fakes = [FakeStages(cfg) for _ in range(world)]
+    xs = [torch.randn(M, cfg["E"], generator=g) for _ in range(world)]
+    sent = []
+    for s in range(world):
+        sel_asc, _, pair_rows, counts, pair_index = fakes[s].ep_route(0, xs[s], 0, defer_shared=True, n_ranks=world, capacity=cap)
+        owner = (sel_asc.to(torch.int64) // epr)              # [M][NU]
+        flag = torch.zeros(M, world, dtype=torch.bool)
+        flag.scatter_(1, owner, True)
+        slot = torch.cumsum(flag.to(torch.int64), 0) - 1      # rank of the token among the destination's tokens
+        slot[~flag] = -1
+        assert int(flag.sum(0).max()) <= cap_t
+        tokrows = torch.full((world * cap_t, cfg["E"]), float("nan"))
+        for t in range(M):
+            for r in range(world):
+                if flag[t, r]:
+                    tokrows[r * cap_t + slot[t, r]] = (xs[s] * 2.0)[t]       # the fake's routed-input row of token t
+        tokidx = torch.zeros(world * cap, dtype=torch.int64)
+        pi = pair_index.to(torch.int64).view(M, NU)
+        for t in range(M):
+            for k in range(NU):
+                tokidx[pi[t, k]] = slot[t, owner[t, k]]
+        sent.append((pair_rows, counts, tokrows, tokidx))
+        assert (flag.sum(0) < NU * M // world + M).all() and int(flag.sum()) < M * NU      # fewer rows than pairs
+    counts_all = torch.stack([c for _, c, _, _ in sent])
+    for r in range(world):
+        pair_recv = torch.cat([sent[s][0][r * cap:(r + 1) * cap] for s in range(world)])     # what pair rows would deliver
+        tok_recv = torch.cat([sent[s][2][r * cap_t:(r + 1) * cap_t] for s in range(world)])
+        idx_recv = torch.cat([sent[s][3][r * cap:(r + 1) * cap] for s in range(world)])
+        off, row_index = fakes[r].ep_recv_layout(counts_all, r, cap)
+        total = int(off[(r + 1) * epr])
+        a = row_index[:total].to(torch.int64)                 # arrival slot of every sorted position
+        in_index = (a // cap) * cap_t + idx_recv[a]
+        assert torch.equal(tok_recv[in_index], pair_recv[a])
+        assert not torch.isnan(tok_recv[in_index]).any()
