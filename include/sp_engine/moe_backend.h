@@ -173,7 +173,13 @@ int sp_moe_ep_finish_dev(sp_moe *h, int layer, int M, const float *x_dev, const 
  *                       that does not fit is reported by sp_moe_status; rerun with capacity_rows = 0.
  *   capacity_rows == 0: exact exchange - split sizes read on the host once per layer (the call synchronises).
  * Needs max_expert_rows of the config >= n_ranks * capacity (padded) or the rows this rank can receive (exact).
- * The first call allocates the exchange buffers (make it before any capture). Bit-identical to sp_moe_forward_dev. */
+ * The first call allocates the exchange buffers (make it before any capture). Bit-identical to sp_moe_forward_dev.
+ * Every rank must have opened its handle with the same configuration (the buffers are laid out alike everywhere).
+ * In a world of up to four ranks the rows are moved by device-to-device copies into the peers' buffers, which the
+ * first call (outside a capture) maps through CUDA IPC - all ranks of one node - with NCCL left to carry the counts
+ * and a one-int all-reduce; with more ranks, or where the mapping fails on any rank, by NCCL send/recv pairs
+ * (SP_MOE_EP_EXCHANGE=copy|nccl in the environment overrides the choice). In the padded exchange a token's input
+ * row travels once per destination rank, with a slot per pair (SP_MOE_EP_DISPATCH=rows: one row per pair). */
 int sp_moe_ep_forward_dev(sp_moe *h, void *nccl_comm, int n_ranks, int rank, int layer_first, int n_layers, int flavour,
                           int M, const float *x_dev, float *y_dev, int capacity_rows, int slices, void *stream);
 /* rows this rank's experts processed in the last layer of the last sp_moe_ep_forward_dev call */
